@@ -8,6 +8,7 @@ The reference has one built-in default, the path of its Mistral 7B file (src/mai
 """
 from __future__ import annotations
 
+import copy
 from typing import Dict
 
 _MISTRAL = {"architectures": ["MistralForCausalLM"], "model_type": "mistral", "hidden_act": "silu",
@@ -80,6 +81,29 @@ PRESETS["sifasun-7b-sizes"] = _sifasun(4096, 32000, 32, 32, 8, 128, 14336, 4096,
 # the same at the sizes of Mistral NeMo 12B (width 5,120, a vocabulary of 131,072)
 PRESETS["sifasun-12b-sizes"] = _sifasun(5120, 131072, 40, 32, 8, 128, 14336, 5120, 16, 2048)
 PRESETS["sifasun-tiny"] = _sifasun(96, 320, 8, 4, 2, 16, 160, 64, 4, 24, shared_from=4)
+
+
+def _kuvelix(width, vocab, layers, heads, kv_heads, dim, vdim, ff, experts, identity, top, groups, keep, expert_ff, loop=None):
+    """A Kuvelix configuration: a dense layer first, then mixture-of-experts layers, every fourth layer without a
+    feed-forward when there are more than four; `loop` = (start, stop, times)."""
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5,
+             "rot": {"base": 10000.0, "dims": dim // 2, "scaling": {"factor": 4.0}}}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0},
+           "router": {"experts": experts, "identity": identity, "top": top, "groups": {"count": groups, "keep": keep}}}
+    out = []
+    for i in range(layers):
+        mlp = {"kind": "dense", "ff": ff} if i == 0 else (None if layers > 4 and i % 4 == 3 else copy.deepcopy(moe))
+        out.append({"type": "attention", "mixer": copy.deepcopy(mixer), "mlp": mlp})
+    cfg = {"architecture": "Kuvelix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": out}
+    if loop is not None:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+# Kuvelix at the width, head count, head size and total feed-forward size (14 experts of 1,024 = 14,336) of Mistral 7B, and
+# a tiny one that runs anywhere in seconds (value size unlike the key size, its layers 1 and 2 run twice).
+PRESETS["kuvelix-7b-sizes"] = _kuvelix(4096, 32000, 32, 32, 8, 128, 128, 14336, 14, 2, 2, 4, 2, 1024)
+PRESETS["kuvelix-tiny"] = _kuvelix(80, 320, 4, 6, 2, 16, 24, 136, 5, 3, 3, 4, 3, 40, loop=(1, 3, 2))
 
 
 def preset(name: str) -> dict:

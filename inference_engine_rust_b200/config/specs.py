@@ -43,7 +43,7 @@ class LayerSpec:
     mixer_prefix: str          # e.g. "model.layers.3.self_attn."
     ffn_prefix: str            # e.g. "model.layers.3.mlp."
     mixer_norm_name: str       # e.g. "model.layers.3.input_layernorm.weight"
-    ffn_norm_name: str         # e.g. "model.layers.3.post_attention_layernorm.weight"
+    ffn_norm_name: str         # e.g. "model.layers.3.post_attention_layernorm.weight"; "": the layer has no second norm
     extra_norms: Mapping[str, Tuple[PartSpec, str]] = field(default_factory=dict)
     block_prefix: str = ""     # where the block arrangement finds tensors of its own, if it has any
 

@@ -56,6 +56,29 @@ class RowScale(Structure):
     _fields_ = [("sumsq", c_void_p), ("parts", c_int), ("hidden", c_int), ("eps", c_float)]
 
 
+class GatedAct(Structure):
+    """Mirror of `IertGatedAct`: out = g' sigmoid(g' (a + b g'^2)) u' with g' = min(g, g_max) and
+    u' = clamp(u, -u_max, u_max) + u_bias."""
+    _fields_ = [("g_max", c_float), ("u_max", c_float), ("u_bias", c_float), ("a", c_float), ("b", c_float)]
+
+
+def gated_act(name: str, limit: Optional[float] = None) -> Optional[GatedAct]:
+    """The constants of a named gated activation: "silu" (None: the kernels' default), "gelu_tanh" (the tanh form
+    of GELU), "clamped_swish" (gate capped at `limit`, up clamped to +-`limit` and shifted by one, sigmoid of
+    1.702 times the gate)."""
+    import math
+    inf = float("inf")
+    if name == "silu":
+        return None
+    if name == "gelu_tanh":
+        c = math.sqrt(2.0 / math.pi)
+        return GatedAct(inf, inf, 0.0, 2.0 * c, 2.0 * c * 0.044715)
+    if name == "clamped_swish":
+        lim = inf if limit is None else float(limit)
+        return GatedAct(lim, lim, 1.0, 1.702, 0.0)
+    raise KernelError(f"gated activation must be one of silu, gelu_tanh, clamped_swish, got {name!r}")
+
+
 def norm_ahead(weight, scaled_out, sumsq_out) -> NormAhead:
     return NormAhead(weight=weight.data_ptr(), weight_dtype=dtype_code(weight.dtype), scaled_out=scaled_out.data_ptr(),
                      ld=scaled_out.stride(0), sumsq_out=sumsq_out.data_ptr(), parts=0)
@@ -95,6 +118,7 @@ def _declare(lib) -> None:
         "iert_rmsnorm": [P, P, c_int, P, c_int, P, c_int, c_int, c_float, S],
         "iert_rope_kv_store": [P, c_int, POINTER(BatchView), POINTER(KvView), P, c_int, c_int, c_int, c_int, P, S],
         "iert_silu_mul": [P, P, c_int, c_int, c_int, S],
+        "iert_gated_act_mul": [P, P, c_int, c_int, c_int, POINTER(GatedAct), S],
         "iert_add_into": [P, P, c_int, c_longlong, S],
         "iert_advance_positions": [P, P, P, c_int, S],
         "iert_gemm_plain": [P, c_int, P, c_int, P, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, S],
@@ -120,7 +144,11 @@ def _declare(lib) -> None:
                                          c_float, P, P, S],
         "iert_latent_decode_tc_plan": [c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)],
         "iert_router_topk": [P, LL, P, c_int, c_int, c_int, P, P, P, S],
-        "iert_moe_scale": [P, c_int, LL, P, c_int, c_int, c_int, S],
+        "iert_moe_scale": [P, c_int, LL, P, c_int, c_int, c_int, P, P, LL, P, c_int, S],
+        "iert_router_grouped": [P, LL, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P, P, P, S],
+        "iert_qkv_prep": [P, LL, P, P, c_int, POINTER(BatchView), POINTER(KvView), c_int, c_int, c_int, P, c_int, c_int, P, P,
+                          c_float, c_int, P, S],
+        "iert_gate_mul": [P, P, LL, P, c_int, c_int, c_int, c_int, c_int, S],
         "iert_add_normed": [P, P, P, P, c_int, c_int, c_int, c_float, S],
         "iert_cast_rows": [P, P, P, c_int, LL, S],
         "iert_scale_values": [P, LL, c_float, S],
@@ -134,8 +162,8 @@ def _declare(lib) -> None:
     lib.iert_attention_decode.restype = c_int
     lib.iert_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.iert_attention_decode_scratch_floats.restype = c_longlong
-    lib.iert_gemm_tc_gated.argtypes = [P, c_longlong, P, c_longlong, P, c_longlong, c_int, c_int, c_int, c_int,
-                                       c_int, P, S]
+    lib.iert_gemm_tc_gated.argtypes = [P, c_longlong, P, c_longlong, P, c_longlong, c_int, c_int, c_int, POINTER(GatedAct),
+                                       c_int, c_int, P, S]
     lib.iert_gemm_tc_gated.restype = c_int
     lib.iert_gemm_rows.argtypes = [P, c_longlong, P, c_longlong, P, c_int, c_longlong, c_int, c_int, c_int, c_int,
                                    POINTER(RowScale), POINTER(NormAhead), c_int, P, S]
@@ -144,7 +172,7 @@ def _declare(lib) -> None:
                                         P, c_longlong, P, c_int, POINTER(RowScale), POINTER(NormAhead), c_int, c_int, P, S]
     lib.iert_gemm_tc_scaled.restype = c_int
     lib.iert_gemm_tc_gated_scaled.argtypes = [P, c_longlong, P, c_longlong, P, c_longlong, c_int, c_int, c_int,
-                                              POINTER(RowScale), c_int, P, S]
+                                              POINTER(RowScale), POINTER(GatedAct), c_int, P, S]
     lib.iert_gemm_tc_gated_scaled.restype = c_int
     lib.iert_gemm_tc_workspace_bytes.restype = c_longlong
     lib.iert_gemm_tc_counter_count.restype = c_int
@@ -256,6 +284,12 @@ def rotate_qk(qkv, batch: BatchView, inv_freq, heads: int, kv_heads: int, head_d
 def silu_mul(gu, out, n_tokens: int, inter: int, stream) -> None:
     check(core().iert_silu_mul(gu.data_ptr(), out.data_ptr(), dtype_code(gu.dtype), n_tokens, inter,
                                stream), "silu_mul")
+
+
+def gated_act_mul(gu, out, n_tokens: int, inter: int, act: GatedAct, stream) -> None:
+    """out[t, i] = f(gu[t, i], gu[t, inter + i]) for f of the gated-activation family."""
+    check(core().iert_gated_act_mul(gu.data_ptr(), out.data_ptr(), dtype_code(gu.dtype), n_tokens, inter, byref(act), stream),
+          "gated_act_mul")
 
 
 def add_into(residual, y, n: int, stream) -> None:
@@ -388,13 +422,14 @@ def gemm_tc_scaled(x, w, out, M: int, mode: int, err, stream, scale: Optional[Ro
     return True
 
 
-def gemm_tc_gated_scaled(x, w, act, M: int, scale: RowScale, err, stream, force_bt: int = 0) -> bool:
+def gemm_tc_gated_scaled(x, w, act, M: int, scale: RowScale, err, stream, force_bt: int = 0,
+                         fn: Optional[GatedAct] = None) -> bool:
     """`gemm_tc_gated` in its one-token form for an x that is the first half of an RMSNorm: gate and
     up are multiplied by the rows' 1 / rms before the activation."""
     two_i, K = w.shape
     status = core().iert_gemm_tc_gated_scaled(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), act.data_ptr(),
-                                              act.stride(0), M, two_i // 2, K, byref(scale), force_bt,
-                                              err.data_ptr(), stream)
+                                              act.stride(0), M, two_i // 2, K, byref(scale),
+                                              byref(fn) if fn is not None else None, force_bt, err.data_ptr(), stream)
     if status == 1:
         return False
     check(status, "gemm_tc_gated_scaled")
@@ -532,14 +567,15 @@ def attention_decode_tc_rope(qkv, out, batch: BatchView, kv: KvView, heads: int,
     return True
 
 
-def gemm_tc_gated(x, w, act, M: int, err, stream, force_bt: int = 0, force_stages: int = 0) -> bool:
-    """act[:M] = silu(x @ w[:I].T) * (x @ w[I:].T) for w = [gate; up] with 2 I rows, on the tensor
-    cores in one kernel.  Returns False, having launched nothing, when the operands do not meet
-    the kernel's alignment rules."""
+def gemm_tc_gated(x, w, act, M: int, err, stream, force_bt: int = 0, force_stages: int = 0,
+                  fn: Optional[GatedAct] = None) -> bool:
+    """act[:M] = f(x @ w[:I].T, x @ w[I:].T) for w = [gate; up] with 2 I rows and f of the gated-activation family
+    (`fn`; None: silu(gate) * up), on the tensor cores in one kernel.  Returns False, having launched nothing, when the
+    operands do not meet the kernel's alignment rules."""
     two_i, K = w.shape
     status = core().iert_gemm_tc_gated(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), act.data_ptr(),
-                                       act.stride(0), M, two_i // 2, K, force_bt, force_stages,
-                                       err.data_ptr(), stream)
+                                       act.stride(0), M, two_i // 2, K, byref(fn) if fn is not None else None,
+                                       force_bt, force_stages, err.data_ptr(), stream)
     if status == 1:
         return False
     check(status, "gemm_tc_gated")
@@ -701,9 +737,20 @@ def router_topk(z, bias, n_tokens: int, E: int, top: int, wt, idx, w, stream) ->
                                   w.data_ptr(), stream), "router_topk")
 
 
-def moe_scale(act, wt, n_tokens: int, E: int, F: int, stream) -> None:
-    check(core().iert_moe_scale(act.data_ptr(), dtype_code(act.dtype), act.stride(0), wt.data_ptr(), n_tokens, E, F, stream),
-          "moe_scale")
+def router_grouped(z, correction, n_tokens: int, E: int, N: int, top: int, groups: int, keep: int, wt, wid, idx, w,
+                   stream) -> None:
+    """Scores = softmax over all N router outputs (the last N - E stand for experts that return their input); choice on
+    score + correction inside the `keep` best of `groups` runs of neighbours; weights = chosen scores over their sum.
+    wt [T, E] dense, wid [T] the identity experts' share, idx / w [T, top]."""
+    check(core().iert_router_grouped(z.data_ptr(), z.stride(0), _ptr(correction), n_tokens, E, N, top, groups, keep,
+                                     wt.data_ptr(), wid.data_ptr(), idx.data_ptr(), w.data_ptr(), stream), "router_grouped")
+
+
+def moe_scale(act, wt, n_tokens: int, E: int, F: int, stream, wid=None, x=None, residual=None) -> None:
+    """act[t, e*F + i] *= wt[t, e]; with `wid`, also residual[t] += wid[t] * x[t]."""
+    check(core().iert_moe_scale(act.data_ptr(), dtype_code(act.dtype), act.stride(0), wt.data_ptr(), n_tokens, E, F,
+                                _ptr(wid), _ptr(x), x.stride(0) if x is not None else 0, _ptr(residual),
+                                residual.shape[-1] if residual is not None else 0, stream), "moe_scale")
 
 
 # ---------------------------------------------------------------------------------------
@@ -738,6 +785,23 @@ def qk_prep(proj, qkv, batch: BatchView, kv: KvView, heads: int, inv_freq, rotar
     check(core().iert_qk_prep(proj.data_ptr(), proj.stride(0), qkv.data_ptr(), dtype_code(qkv.dtype), byref(batch), byref(kv),
                               heads, inv_freq.data_ptr(), rotary_dim, norm_mode, _ptr(wq), _ptr(wk), eps, value_scale,
                               1 if store else 0, err.data_ptr(), stream), "qk_prep")
+
+
+def qkv_prep(proj, bias, qkv, batch: BatchView, kv: KvView, heads: int, dim: int, vdim: int, inv_freq, rotary_dim: int,
+             pairing: int, wq, wk, eps: float, store: bool, err, stream) -> None:
+    """From the fp32 projection rows that begin with [q | k | v] (+ `bias`) to the packed rows [q' | k' | v'] with every
+    head padded with zeros to the cache's head size: per-head weighted RMS norm of q and k (`wq`, `wk` of length `dim`,
+    optional), rotation, one rounding, and the cache write of k' and v'."""
+    check(core().iert_qkv_prep(proj.data_ptr(), proj.stride(0), _ptr(bias), qkv.data_ptr(), dtype_code(qkv.dtype), byref(batch),
+                               byref(kv), heads, dim, vdim, _ptr(inv_freq), rotary_dim, pairing, _ptr(wq), _ptr(wk), eps,
+                               1 if store else 0, err.data_ptr(), stream), "qkv_prep")
+
+
+def gate_mul(attn, gate, out, n_tokens: int, heads: int, D: int, vdim: int, stream) -> None:
+    """out[t, h*vdim + c] = attn[t, h*D + c] * sigmoid(gate[t, h*vdim + c]); `gate` (fp32, a view whose rows may be
+    strided) may be None: the padding of the heads is dropped and nothing else."""
+    check(core().iert_gate_mul(attn.data_ptr(), _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(),
+                               dtype_code(attn.dtype), n_tokens, heads, D, vdim, stream), "gate_mul")
 
 
 def rglru_conv(proj, bx, taps, cb, state, u, C: int, K: int, batch: BatchView, stream) -> None:

@@ -36,7 +36,7 @@ CORE_SOURCES = [
     "runtime.cu", "elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu",
     "gemm_tc.cu", "gemm_rows.cu", "attention_decode.cu",
     "streams_norm.cu", "recurrent_prep.cu", "latent_attention.cu", "latent_decode_tc.cu", "moe.cu",
-    "outnorm.cu", "qk_prep.cu", "rglru.cu",
+    "outnorm.cu", "qk_prep.cu", "rglru.cu", "qkv_prep.cu",
 ]
 # the native reader of weight files (host code), loaded by the weights package
 IO_SOURCES = ["weight_reader.cu"]

@@ -87,6 +87,16 @@ struct IertRowScale {
   float eps;
 };
 
+// The activation of a gated feed-forward as one family with five constants:
+//   g' = min(g, g_max);   u' = clamp(u, -u_max, u_max) + u_bias;   out = g' * sigmoid(g' * (a + b * g'^2)) * u'
+// SiLU-gated:            g_max = u_max = +inf, u_bias = 0, a = 1, b = 0
+// tanh-form GELU-gated:  0.5 g (1 + tanh(c (g + 0.044715 g^3))) = g * sigmoid(2c g (1 + 0.044715 g^2)), c = sqrt(2 / pi):
+//                        a = 2c, b = 0.08943 c
+// clamped swish-gated:   g_max = u_max = limit, u_bias = 1, a = 1.702, b = 0
+struct IertGatedAct {
+  float g_max, u_max, u_bias, a, b;
+};
+
 namespace iert {
 
 // 1 / sqrt(mean + eps) of up to `n_tokens` rows from their partial sums of squares into out[t]
@@ -132,6 +142,19 @@ template <typename T> __device__ __forceinline__ T from_f32(float x);
 template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) {
   return __float2bfloat16_rn(x);
+}
+
+// out of the gated-activation family above; `fast`: approximate exponential and division (bfloat16 results)
+template <bool FAST>
+__device__ __forceinline__ float gated_act(float g, float u, const IertGatedAct& a) {
+  g = fminf(g, a.g_max);
+  u = fminf(fmaxf(u, -a.u_max), a.u_max) + a.u_bias;
+  const float z = g * fmaf(a.b, g * g, a.a);
+  if (FAST) return __fdividef(g * u, 1.0f + __expf(-z));
+  // the stable branch of the sigmoid
+  const float e = expf(-fabsf(z));
+  const float sg = z >= 0.f ? 1.0f / (1.0f + e) : e / (1.0f + e);
+  return g * sg * u;
 }
 
 // A soft cap on an attention score, in base-2 units: c log2(e) tanh(raw * scale / c), with

@@ -434,6 +434,67 @@ IERT_API int iert_silu_mul(const void* gu, void* out, int dtype, int n_tokens, i
   return iert_check_launch("silu_mul");
 }
 
+// The same for any activation of the gated family (IertGatedAct): out[t, i] = f(gu[t, i], gu[t, I+i]).
+template <typename T>
+__global__ void gated_act_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total, IertGatedAct fn) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / inter;
+    const int i = (int)(idx - t * inter);
+    out[idx] = from_f32<T>(gated_act<false>(to_f32(gu[t * 2 * inter + i]), to_f32(gu[t * 2 * inter + inter + i]), fn));
+  }
+}
+
+__global__ void gated_act_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int inter,
+                                            size_t total8, IertGatedAct fn) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int per_row = inter / 8;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / per_row;
+    const int i = (int)(idx - t * per_row) * 8;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + i);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + inter + i);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 g = __bfloat1622float2(gp[e]), u = __bfloat1622float2(up[e]);
+      op[e] = __floats2bfloat162_rn(gated_act<false>(g.x, u.x, fn), gated_act<false>(g.y, u.y, fn));
+    }
+    *reinterpret_cast<uint4*>(out + t * inter + i) = o4;
+  }
+}
+
+IERT_API int iert_gated_act_mul(const void* gu, void* out, int dtype, int n_tokens, int inter, const IertGatedAct* fn,
+                                cudaStream_t stream) {
+  if (n_tokens <= 0) return IERT_OK;
+  if (inter <= 0 || !fn) return IERT_BAD_ARGUMENT;
+  const size_t total = (size_t)n_tokens * inter;
+  const int threads = 256;
+  if (dtype == IERT_BF16 && inter % 8 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    const size_t total8 = total / 8;
+    const size_t want = (total8 + threads - 1) / threads;
+    const size_t cap = (size_t)iert_sm_count_cached() * 32;
+    launch_dep(gated_act_mul_bf16x8_kernel, (int)(want < cap ? want : cap), threads, 0, stream, (const __nv_bfloat16*)gu,
+               (__nv_bfloat16*)out, inter, total8, *fn);
+    return iert_check_launch("gated_act_mul");
+  }
+  const size_t cap16 = (size_t)iert_sm_count_cached() * 16;
+  const int blocks = (int)((total + threads - 1) / threads < cap16 ? (total + threads - 1) / threads : cap16);
+  if (dtype == IERT_F32)
+    launch_dep(gated_act_mul_kernel<float>, blocks, threads, 0, stream, (const float*)gu, (float*)out, inter, total, *fn);
+  else if (dtype == IERT_BF16)
+    launch_dep(gated_act_mul_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
+               inter, total, *fn);
+  else
+    return IERT_BAD_ARGUMENT;
+  return iert_check_launch("gated_act_mul");
+}
+
 // ---------------------------------------------------------------------------------------
 // residual[i] += y[i] in fp32 (src/ops/residual_add.rs:3-12).  Used by parts whose last
 // kernel cannot add into the residual stream itself.

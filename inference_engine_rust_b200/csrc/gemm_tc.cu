@@ -83,6 +83,7 @@ struct GemmParams {
                         // the rows' 1 / rms
   IertNormAhead ahead;  // split-K residual add, tiles of 32 or 64 tokens: ahead.scaled_out != null: the reduction also
                         // writes the next norm's first half
+  IertGatedAct act;     // gated launches: the activation (see common.cuh)
   int trace_seq;        // >= 0: the launch's row in the trace (builds with IERT_GEMM_TRACE only)
   uint32_t poll_limit;  // polls of a tile's counter before a CTA gives up waiting for the other CTAs of its tile
 };
@@ -147,11 +148,9 @@ __device__ __forceinline__ void write_out4(const GemmParams& p, int tok, int n, 
   }
 }
 
-// silu(g) * u = g * u / (1 + e^-g).  One exponential and one reciprocal per element (for very
-// negative g the exponential overflows to +inf and the quotient is 0, which is the limit).
-__device__ __forceinline__ float silu_mul(float g, float u) {
-  return __fdividef(g * u, 1.0f + __expf(-g));
-}
+// The gated activation (see IertGatedAct; SiLU: g * u / (1 + e^-g)).  One exponential and one reciprocal per
+// element (for a very negative argument the exponential overflows to +inf and the quotient is 0, which is the limit).
+#define silu_mul(g, u) gated_act<true>((g), (u), p.act)
 
 // Split-K: rows t_first, t_first + 4, ... < t_end of a tile's partial products (one [BT][TILE_N]
 // fp32 block per split at `base`) added in split order and written out; 32 threads share a row, each
@@ -1172,13 +1171,13 @@ IERT_API int iert_gemm_tc_scaled(const void* x, long long ldx, const void* w, lo
                       force_splits, 0, scale, ahead, err, stream);
 }
 
-// act[t, i] = silu(x[t] . w[i]) * (x[t] . w[inter + i]) for w = [gate; up] of 2 * inter rows,
-// in one kernel (two accumulators per tile).  act: bf16 [M, inter], row stride ldo.  Whole
+// act[t, i] = f(x[t] . w[i], x[t] . w[inter + i]) for w = [gate; up] of 2 * inter rows and f of the gated-activation
+// family (`fn`; null: silu(gate) * up), in one kernel (two accumulators per tile).  act: bf16 [M, inter], row stride ldo.  Whole
 // tiles only; same alignment rules as iert_gemm_tc.
 namespace {
 int gemm_tc_gated_impl(const void* x, long long ldx, const void* w, long long ldw, void* act,
-                       long long ldo, int M, int inter, int K, const IertRowScale* scale, int force_bt, int force_stages,
-                       int* err, cudaStream_t stream) {
+                       long long ldo, int M, int inter, int K, const IertRowScale* scale, const IertGatedAct* fn, int force_bt,
+                       int force_stages, int* err, cudaStream_t stream) {
   if (M <= 0 || inter <= 0) return IERT_OK;
   if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
     return IERT_BAD_ARGUMENT;
@@ -1187,6 +1186,7 @@ int gemm_tc_gated_impl(const void* x, long long ldx, const void* w, long long ld
   p.scale = IertRowScale{nullptr, 0, 0, 0.f};
   p.tail_parts = 1; p.full_tiles = 0; p.tma_out = 0; p.t_group = 1 << 30;
   p.out = act; p.ldo = ldo; p.out_dtype = IERT_BF16; p.mode = MODE_GATED_SILU;
+  p.act = fn ? *fn : IertGatedAct{INFINITY, INFINITY, 0.f, 1.f, 0.f};
   p.M = M; p.N = inter; p.K = K;
   const bool weight_major = force_bt ? (force_bt != 128 && M <= force_bt)
                                      : (M <= 64 && (inter + TILE_N / 2 - 1) / (TILE_N / 2) >= sm_count());
@@ -1244,17 +1244,17 @@ int gemm_tc_gated_impl(const void* x, long long ldx, const void* w, long long ld
 }  // namespace
 
 IERT_API int iert_gemm_tc_gated(const void* x, long long ldx, const void* w, long long ldw, void* act,
-                                long long ldo, int M, int inter, int K, int force_bt, int force_stages,
+                                long long ldo, int M, int inter, int K, const IertGatedAct* fn, int force_bt, int force_stages,
                                 int* err, cudaStream_t stream) {
-  return gemm_tc_gated_impl(x, ldx, w, ldw, act, ldo, M, inter, K, nullptr, force_bt, force_stages, err, stream);
+  return gemm_tc_gated_impl(x, ldx, w, ldw, act, ldo, M, inter, K, nullptr, fn, force_bt, force_stages, err, stream);
 }
 
 // The one-token form (M <= 64) for an x that is the first half of an RMSNorm (IertNormAhead of the kernel
 // that wrote it): gate and up are multiplied by each row's 1 / rms before the activation.
 // IERT_BAD_ARGUMENT, nothing launched, where the one-token form does not apply.
 IERT_API int iert_gemm_tc_gated_scaled(const void* x, long long ldx, const void* w, long long ldw, void* act,
-                                       long long ldo, int M, int inter, int K, const IertRowScale* scale, int force_bt,
-                                       int* err, cudaStream_t stream) {
+                                       long long ldo, int M, int inter, int K, const IertRowScale* scale,
+                                       const IertGatedAct* fn, int force_bt, int* err, cudaStream_t stream) {
   if (!scale) return IERT_BAD_ARGUMENT;
-  return gemm_tc_gated_impl(x, ldx, w, ldw, act, ldo, M, inter, K, scale, force_bt, 0, err, stream);
+  return gemm_tc_gated_impl(x, ldx, w, ldw, act, ldo, M, inter, K, scale, fn, force_bt, 0, err, stream);
 }

@@ -31,7 +31,8 @@ class Model:
         for ls in spec.layers:
             norm_cls = part_class("norm", ls.norm.kind)
             norm1 = norm_cls(ls.norm, h, rt)
-            norm2 = norm_cls(ls.norm, h, rt) if ls.ffn is not None else None
+            # an arrangement whose feed-forward reads the first norm names no second one (`ffn_norm_name` empty)
+            norm2 = norm_cls(ls.norm, h, rt) if ls.ffn is not None and ls.ffn_norm_name else None
             mixer = part_class("mixer", ls.mixer.kind)(ls.mixer, rt)
             ffn = part_class("ffn", ls.ffn.kind)(ls.ffn, rt) if ls.ffn is not None else None
             extra = {role: part_class("norm", ns.kind)(ns, h, rt) for role, (ns, _) in ls.extra_norms.items()}
@@ -87,7 +88,8 @@ class Model:
             for local, ts in mixer.tensor_specs().items():
                 out[ls.mixer_prefix + local] = ts
             if ffn is not None:
-                out.update(self._norm_specs(norm2, ls.ffn_norm_name))
+                if norm2 is not None:
+                    out.update(self._norm_specs(norm2, ls.ffn_norm_name))
                 for local, ts in ffn.tensor_specs().items():
                     out[ls.ffn_prefix + local] = ts
             for role, norm in extra.items():
@@ -143,7 +145,8 @@ class Model:
             load_norm(norm1, ls.mixer_norm_name)
             mixer.load({local: get(ls.mixer_prefix + local) for local in mixer.tensor_specs()})
             if ffn is not None:
-                load_norm(norm2, ls.ffn_norm_name)
+                if norm2 is not None:
+                    load_norm(norm2, ls.ffn_norm_name)
                 ffn.load({local: get(ls.ffn_prefix + local) for local in ffn.tensor_specs()})
             for role, norm in extra.items():
                 load_norm(norm, ls.extra_norms[role][1])

@@ -1,4 +1,5 @@
-"""Arrangement of a layer's parts.  "prenorm": x += mixer(norm1(x)); x += ffn(norm2(x)) (the second
+"""Arrangement of a layer's parts.  "shared_norm": h = norm1(x); x += mixer(h) + ffn(h) (one norm, read by both
+sublayers).  "prenorm": x += mixer(norm1(x)); x += ffn(norm2(x)) (the second
 half left out for a layer without a feed-forward)
 (src/layers/block.rs:19-24,63-65; the residual uses the un-normed input,
 src/layers/attention.rs:757-759, src/layers/ffn.rs:113-116)."""
@@ -166,6 +167,37 @@ class OutputNormBlock(Block):
         ctx.rows_ahead = CastAhead(x, h, y)
 
 
+class SharedNormBlock(Block):
+    """One norm, read by both sublayers, whose results are added to the same residual:
+
+        h = norm1(x);   x <- x + mixer(h) + ffn(h)             (the feed-forward left out for a layer without one)
+
+    The layer has no second norm (`LayerSpec.ffn_norm_name` is empty).  Both sublayers add into the fp32 residual;
+    neither reads it, so the order of the two additions is free.  The norm runs as a kernel of its own: its input
+    rows change under the second sublayer's eyes (the first has added its result by then), so a norm split around a
+    kernel boundary (`NormRequest`) would have to be finished from a copy, which the block's own kernel already is."""
+    graph_safe = True
+
+    def __init__(self, layer_spec, norm1, mixer, norm2, ffn, rt: Runtime):
+        if norm2 is not None:
+            raise ValueError("block 'shared_norm' has one norm; leave LayerSpec.ffn_norm_name empty")
+        self.norm1, self.mixer, self.ffn, self.rt = norm1, mixer, ffn, rt
+
+    def forward(self, x, ctx: StepContext, cache_view, writes_cache: bool) -> None:
+        ctx.rows_ahead = None
+        h = self.rt.workspace.take("block.normed", x.shape, self.rt.dtype)
+        self.norm1.forward(x, h, ctx, rows=ctx.n_tokens)
+        # only the block's last addition may write the next block's norm ahead: the rows are final then
+        ahead = first_norm_request_of(ctx.next_block, ctx)
+        ctx.norm_ahead = ahead if self.ffn is None else None
+        self.mixer.forward(h, x, ctx, cache_view, writes_cache)
+        if self.ffn is not None:
+            ctx.norm_ahead = ahead
+            self.ffn.forward(h, x, ctx)
+        ctx.norm_ahead = None
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "shared_norm", SharedNormBlock)
 register_part("block", "outnorm", OutputNormBlock)
 register_part("block", "hyper", HyperConnectionBlock)

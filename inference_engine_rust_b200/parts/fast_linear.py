@@ -70,9 +70,9 @@ def apply(linear, x, out, n_rows: int, mode: int, stream: int, ctx=None) -> bool
     return B.gemm_tc(x, linear.weight, out, n_rows, mode, err, stream)
 
 
-def apply_gated(linear, x, act, n_rows: int, stream: int) -> bool:
-    """act = silu(x . Wgate^T) * (x . Wup^T) in one kernel, for a row-concatenated
-    [gate; up] weight.  False means the caller runs product and activation separately.  An `x`
+def apply_gated(linear, x, act, n_rows: int, stream: int, fn=None) -> bool:
+    """act = silu(x . Wgate^T) * (x . Wup^T) (or another activation of the gated family: `fn`, a
+    `bindings.GatedAct`) in one kernel, for a row-concatenated [gate; up] weight.  False means the caller runs product and activation separately.  An `x`
     that is the first half of a norm (`ScaledRows`) is taken by the one-token form only."""
     from .norm import ScaledRows
     if linear.weight.dtype != torch.bfloat16 or act.dtype != torch.bfloat16:
@@ -87,7 +87,8 @@ def apply_gated(linear, x, act, n_rows: int, stream: int) -> bool:
         if n_rows > GATED_MAX_DECODE_ROWS or -(-(linear.weight.shape[0] // 2) // 64) < B.sm_count():
             return False
         if scaled is not None:
-            return B.gemm_tc_gated_scaled(scaled.scaled, linear.weight, act, n_rows, scaled.row_scale(), linear.rt.err, stream)
+            return B.gemm_tc_gated_scaled(scaled.scaled, linear.weight, act, n_rows, scaled.row_scale(), linear.rt.err, stream,
+                                          fn=fn)
     elif scaled is not None:
         return False
-    return B.gemm_tc_gated(x, linear.weight, act, n_rows, linear.rt.err, stream)
+    return B.gemm_tc_gated(x, linear.weight, act, n_rows, linear.rt.err, stream, fn=fn)

@@ -1,4 +1,5 @@
-"""Dense gated feed-forward: y = (silu(x Wg^T) * (x Wu^T)) Wd^T, added to the block input
+"""Dense gated feed-forward: y = (act(x Wg^T) * (x Wu^T)) Wd^T with act = SiLU (or, by the spec's `activation`,
+another member of the gated-activation family: "gelu_tanh", "clamped_swish" with its `limit`), added to the block input
 (src/layers/ffn.rs:35-63,113-116; src/ops/swiglu.rs:3-36).  Gate and up are one product
 against the row-concatenated matrix [gate_proj; up_proj]: output columns [0, I) are the
 gate, [I, 2I) the up projection, which is what the activation kernel indexes."""
@@ -24,6 +25,8 @@ class SwiGLU(FeedForward):
         self.intermediate_size = int(spec["intermediate_size"])
         # local tensor names of (gate, up, down); an architecture whose files name them otherwise says so
         self.names = tuple(spec.get("tensor_names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
+        # None: SiLU, which every kernel has built in
+        self.act = B.gated_act(spec.get("activation", "silu"), spec.get("limit"))
         self.gate_up = None
         self.down = None
 
@@ -48,11 +51,14 @@ class SwiGLU(FeedForward):
         done = False
         if rt.fast:
             from . import fast_linear
-            done = fast_linear.apply_gated(self.gate_up, xn, act, T, ctx.stream)
+            done = fast_linear.apply_gated(self.gate_up, xn, act, T, ctx.stream, fn=self.act)
         if not done:
             gu = ws.take("ffn.gate_up", (T, 2 * I), rt.dtype)
             self.gate_up.apply(xn, gu, T, ctx.stream)
-            B.silu_mul(gu, act, T, I, ctx.stream)
+            if self.act is None:
+                B.silu_mul(gu, act, T, I, ctx.stream)
+            else:
+                B.gated_act_mul(gu, act, T, I, self.act, ctx.stream)
         self.down.apply(act, residual, T, ctx.stream, add_residual=True, ctx=ctx)
 
 
