@@ -444,7 +444,7 @@ def main() -> int:
     ap.add_argument("--kernels", action="store_true",
                     help="also time the dominant kernels one by one with CUDA events (projections and decode "
                          "attention at the decode batch, projections at the prefill length): key 'kernels'")
-    ap.add_argument("--design", default=None, choices=["vefulix", "sifasun"],
+    ap.add_argument("--design", default=None, choices=["vefulix", "sifasun", "kuvelix"],
                     help="instead of the default workload: prefill and decode of that design at Mistral 7B's width, "
                          "depth (--layers, default 8) and feed-forward size beside Mistral 7B itself, with a table of "
                          "each step's kernels against what their bytes and FLOPs allow (one JSON line)")
@@ -454,8 +454,8 @@ def main() -> int:
 
     if a.design is not None and a.impl != "reference":
         from inference_engine_rust_b200 import bench_designs
-        if a.design_sizes == "12b" and a.design != "sifasun":
-            ap.error("--design-sizes 12b is there for --design sifasun only")
+        if a.design_sizes == "12b" and a.design not in ("sifasun", "kuvelix"):
+            ap.error("--design-sizes 12b is there for --design sifasun and --design kuvelix only")
         base = "7b-v0.1" if a.design_sizes == "7b" else "nemo-12b"
         print(json.dumps(bench_designs.compare(f"{a.design}-{a.design_sizes}-sizes", base, a.layers or 8, peaks(), a.batch, a.context,
                                                a.prefill_tokens, min(a.steps, 32), max(3, min(a.warmup, 4)))))

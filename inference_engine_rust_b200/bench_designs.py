@@ -19,7 +19,7 @@ LAUNCHERS = ["embed_gather", "rmsnorm", "rope_kv_store", "silu_mul", "gemm_plain
              "attention_decode", "attention_plain", "streams_norm", "streams_expand", "softcap", "delta_prep", "delta_recur",
              "mlstm_recur", "gated_head_norm", "latent_norm_store", "latent_attention_prompt", "latent_attention_decode_tc",
              "latent_attention_decode", "router_topk", "moe_scale", "add_normed", "cast_rows", "scale_values", "qk_prep",
-             "rglru_conv", "rglru_gates", "rglru_scan"]
+             "rglru_conv", "rglru_gates", "rglru_scan", "qkv_prep", "gate_mul", "router_grouped", "gated_act_mul"]
 GEMMS = {"gemm_plain", "gemm_tc", "gemm_rows", "gemm_tc_scaled", "gemm_tc_gated", "gemm_tc_gated_scaled"}
 
 
@@ -144,6 +144,22 @@ def _costs(cfg: dict, T: int, n_seqs: int, ctx: int, prompt: bool) -> Dict[str, 
             out["rglru_conv"] = (0.0, False, T * C * 8)
             out["rglru_gates"] = (4.0 * T * C * bw, False, T * C * 12 + 2 * C * bw * 2)
             out["rglru_scan"] = (0.0, False, T * C * 14 + n_seqs * C * r["conv"] * 8)
+    elif cfg.get("architecture") == "Kuvelix":
+        H = cfg["width"]
+        m = cfg["layers"][0]["mixer"]
+        D = -(-max(m["dim"], m["vdim"]) // 16) * 16                      # the padded head size of the packed rows
+        qd, kd, vd, ad = m["heads"] * m["dim"], m["kv_heads"] * m["dim"], m["kv_heads"] * m["vdim"], m["heads"] * m["vdim"]
+        packed = (m["heads"] + 2 * m["kv_heads"]) * D
+        out["rmsnorm"] = (0.0, False, T * H * 6)
+        out["qkv_prep"] = (0.0, False, T * ((qd + kd + vd) * 4 + packed * 2 + 2 * m["kv_heads"] * D * 2))
+        out["gate_mul"] = (0.0, False, T * (m["heads"] * D * 2 + ad * 4 + ad * 2))
+        out["attention_prefill"] = (4.0 * m["heads"] * D * T * (T + 1) / 2, True, T * (2 * m["heads"] * D + 2 * m["kv_heads"] * D) * 2)
+        out["attention_decode_tc"] = (0.0, False, n_seqs * ctx * 2 * m["kv_heads"] * D * 2)
+        mlp = next((l["mlp"] for l in cfg["layers"] if l["mlp"] and l["mlp"]["kind"] == "moe"), None)
+        if mlp:
+            r = mlp["router"]
+            out["moe_scale"] = (0.0, False, T * (r["experts"] * mlp["expert"]["ff"] * 4 + (10 * H if r.get("identity") else 0)))
+            out["router_grouped"] = (0.0, False, T * (r["experts"] + r.get("identity", 0)) * 8)
     else:
         hd = cfg["num_attention_heads"] * cfg["head_dim"]
         kvd = cfg["num_key_value_heads"] * cfg["head_dim"]

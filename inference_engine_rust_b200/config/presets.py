@@ -103,6 +103,8 @@ def _kuvelix(width, vocab, layers, heads, kv_heads, dim, vdim, ff, experts, iden
 # Kuvelix at the width, head count, head size and total feed-forward size (14 experts of 1,024 = 14,336) of Mistral 7B, and
 # a tiny one that runs anywhere in seconds (value size unlike the key size, its layers 1 and 2 run twice).
 PRESETS["kuvelix-7b-sizes"] = _kuvelix(4096, 32000, 32, 32, 8, 128, 128, 14336, 14, 2, 2, 4, 2, 1024)
+# the same at the sizes of Mistral NeMo 12B (width 5,120, a vocabulary of 131,072)
+PRESETS["kuvelix-12b-sizes"] = _kuvelix(5120, 131072, 40, 32, 8, 128, 128, 14336, 14, 2, 2, 4, 2, 1024)
 PRESETS["kuvelix-tiny"] = _kuvelix(80, 320, 4, 6, 2, 16, 24, 136, 5, 3, 3, 4, 3, 40, loop=(1, 3, 2))
 
 
