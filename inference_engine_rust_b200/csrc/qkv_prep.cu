@@ -103,6 +103,117 @@ qkv_prep_kernel(const float* __restrict__ proj, long long ld, const float* __res
   }
 }
 
+__device__ __forceinline__ void store4(float* p, const float4& v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float4& v) {
+  uint2 w;
+  *reinterpret_cast<__nv_bfloat162*>(&w.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&w.y) = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = w;
+}
+
+// The same for sizes in whole groups of four (dim, vdim, D, the row stride; 16-byte aligned pointers) and the
+// interleaved pairing (or no rotation): a lane holds groups of four consecutive numbers of a head in registers, a pair
+// (2i, 2i+1) lies inside one group, so nothing passes through shared memory but the angles; 16-byte loads, 8- or
+// 16-byte stores.  CH groups per lane: heads of up to CH * 128 numbers.
+template <typename T, int CH>
+__global__ void __launch_bounds__(THREADS)
+qkv_prep_vec_kernel(const float* __restrict__ proj, long long ld, const float* __restrict__ bias, T* __restrict__ qkv,
+                    IertBatchView b, IertKvView c, int heads, int dim, int vdim, const float* __restrict__ inv_freq,
+                    int rotary_dim, const float* __restrict__ wq, const float* __restrict__ wk, float eps, int write_cache,
+                    int* __restrict__ err) {
+  extern __shared__ float sm[];
+  pdl_launch_dependents();
+  const int D = c.head_dim, nkv = c.kv_heads, half = rotary_dim / 2;
+  const int n_heads = heads + 2 * nkv;
+  float* cs = sm;                                      // [half] cos, [half] sin
+  const int t = blockIdx.x;
+  const int s = sequence_of_token(b, t);
+  const int slot = s < 0 ? -1 : b.slot_ids[s];
+  T* out = qkv + (size_t)t * n_heads * D;
+  if (slot < 0) {
+    pdl_wait();
+    if (blockIdx.y == 0)
+      for (int i = threadIdx.x * 4; i < n_heads * D; i += THREADS * 4) store4(out + i, make_float4(0.f, 0.f, 0.f, 0.f));
+    return;
+  }
+  const int q_begin = b.cu_q[s], q_len = b.cu_q[s + 1] - q_begin;
+  const int pos = b.pos0[s] + (t - q_begin);
+  const int final_len = b.pos0[s] + q_len;
+  for (int k = threadIdx.x; k < half; k += THREADS) {
+    float sn, co;
+    sincosf((float)pos * inv_freq[k], &sn, &co);
+    cs[k] = co;
+    cs[half + k] = sn;
+  }
+  pdl_wait();
+  __syncthreads();
+  const bool store = write_cache && pos >= final_len - c.ring_pages * c.page_tokens;
+  const float* pr = proj + (size_t)t * ld;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qd = heads * dim, kd = nkv * dim;
+  for (int h = blockIdx.y * WARPS + warp; h < n_heads; h += gridDim.y * WARPS) {
+    const bool is_v = h >= heads + nkv, is_k = !is_v && h >= heads;
+    const int n = is_v ? vdim : dim;
+    const int src = is_v ? qd + kd + (h - heads - nkv) * vdim : h * dim;
+    float4 x[CH];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+      const int e = 4 * (lane + 32 * j);
+      x[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (e < n) {
+        x[j] = *reinterpret_cast<const float4*>(pr + src + e);
+        if (bias) {
+          const float4 bb = *reinterpret_cast<const float4*>(bias + src + e);
+          x[j].x += bb.x; x[j].y += bb.y; x[j].z += bb.z; x[j].w += bb.w;
+        }
+        ss += x[j].x * x[j].x + x[j].y * x[j].y + x[j].z * x[j].z + x[j].w * x[j].w;
+      }
+    }
+    const float* w = is_v ? nullptr : (is_k ? wk : wq);
+    if (w) {
+      ss = warp_sum(ss);
+      const float r = 1.0f / sqrtf(ss / (float)dim + eps);
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int e = 4 * (lane + 32 * j);
+        if (e < n) {
+          const float4 ww = *reinterpret_cast<const float4*>(w + e);
+          x[j].x = x[j].x * r * ww.x; x[j].y = x[j].y * r * ww.y; x[j].z = x[j].z * r * ww.z; x[j].w = x[j].w * r * ww.w;
+        }
+      }
+    }
+    if (!is_v) {
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int k0 = 2 * (lane + 32 * j);                 // the group's pairs: k0 and k0 + 1
+        if (k0 < half) {
+          const float co = cs[k0], sn = cs[half + k0], a = x[j].x, bb = x[j].y;
+          x[j].x = a * co - bb * sn;
+          x[j].y = bb * co + a * sn;
+        }
+        if (k0 + 1 < half) {
+          const float co = cs[k0 + 1], sn = cs[half + k0 + 1], a = x[j].z, bb = x[j].w;
+          x[j].z = a * co - bb * sn;
+          x[j].w = bb * co + a * sn;
+        }
+      }
+    }
+    T* dst = out + (size_t)h * D;
+    long long off = -1;
+    if (store && (is_k || is_v)) off = kv_row_offset(c, slot, pos, is_k ? h - heads : h - heads - nkv, err);
+    T* cache = is_k ? (T*)c.k : (T*)c.v;
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+      const int e = 4 * (lane + 32 * j);
+      if (e < D) {                                          // beyond n: the zeros the group was set to
+        store4(dst + e, x[j]);
+        if (off >= 0) store4(cache + off + e, x[j]);
+      }
+    }
+  }
+}
+
 template <typename T>
 __global__ void gate_mul_kernel(const T* __restrict__ attn, const float* __restrict__ gate, long long ldg, T* __restrict__ out,
                                 int heads, int D, int vdim, size_t total) {
@@ -167,6 +278,21 @@ IERT_API int iert_qkv_prep(const float* proj, long long ld, const float* bias, v
   // many tokens: a block per token; few: the heads of a token over several blocks, a warp's worth each
   const int groups = batch->n_tokens >= 256 ? 1 : (n_heads + WARPS - 1) / WARPS;
   const dim3 grid(batch->n_tokens, groups);
+  const int elt = dtype == IERT_F32 ? 4 : 2;
+  const bool vec = (pairing == IERT_PAIR_INTERLEAVED || rotary_dim == 0) && dim % 4 == 0 && vdim % 4 == 0 && D % 4 == 0 && D <= 256 &&
+                   ld % 4 == 0 && ((uintptr_t)proj & 15) == 0 && (!bias || ((uintptr_t)bias & 15) == 0) &&
+                   (!wq || (((uintptr_t)wq & 15) == 0 && ((uintptr_t)wk & 15) == 0)) && ((uintptr_t)qkv % (4 * elt)) == 0 &&
+                   ((uintptr_t)cache->k % (4 * elt)) == 0 && ((uintptr_t)cache->v % (4 * elt)) == 0 && (dtype == IERT_F32 || dtype == IERT_BF16);
+  if (vec) {
+    const size_t vsmem = (size_t)rotary_dim * sizeof(float);
+#define GO(T, CH)                                                                                                      \
+    launch_dep(qkv_prep_vec_kernel<T, CH>, grid, dim3(THREADS), vsmem, stream, proj, ld, bias, (T*)qkv, *batch, *cache, heads, dim,  \
+               vdim, inv_freq, rotary_dim, wq, wk, eps, write_cache, err)
+    if (dtype == IERT_F32) { if (D <= 128) GO(float, 1); else GO(float, 2); }
+    else { if (D <= 128) GO(__nv_bfloat16, 1); else GO(__nv_bfloat16, 2); }
+#undef GO
+    return iert_check_launch("qkv_prep");
+  }
   if (dtype == IERT_F32)
     launch_dep(qkv_prep_kernel<float>, grid, dim3(THREADS), smem, stream, proj, ld, bias, (float*)qkv, *batch, *cache, heads, dim,
                vdim, inv_freq, rotary_dim, pairing, wq, wk, eps, write_cache, err);
