@@ -145,7 +145,7 @@ def _declare(lib) -> None:
         "iert_latent_decode_tc_plan": [c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)],
         "iert_router_topk": [P, LL, P, c_int, c_int, c_int, P, P, P, S],
         "iert_moe_scale": [P, c_int, LL, P, c_int, c_int, c_int, P, P, LL, P, c_int, S],
-        "iert_router_grouped": [P, LL, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P, P, P, S],
+        "iert_router_grouped": [P, LL, LL, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P, P, P, S],
         "iert_qkv_prep": [P, LL, P, P, c_int, POINTER(BatchView), POINTER(KvView), c_int, c_int, c_int, P, c_int, c_int, P, P,
                           c_float, c_int, P, S],
         "iert_gate_mul": [P, P, LL, P, c_int, c_int, c_int, c_int, c_int, S],
@@ -738,11 +738,13 @@ def router_topk(z, bias, n_tokens: int, E: int, top: int, wt, idx, w, stream) ->
 
 
 def router_grouped(z, correction, n_tokens: int, E: int, N: int, top: int, groups: int, keep: int, wt, wid, idx, w,
-                   stream) -> None:
+                   stream, by_output: bool = False) -> None:
     """Scores = softmax over all N router outputs (the last N - E stand for experts that return their input); choice on
     score + correction inside the `keep` best of `groups` runs of neighbours; weights = chosen scores over their sum.
-    wt [T, E] dense, wid [T] the identity experts' share, idx / w [T, top]."""
-    check(core().iert_router_grouped(z.data_ptr(), z.stride(0), _ptr(correction), n_tokens, E, N, top, groups, keep,
+    z: fp32 [T, N], or with `by_output` [N, T] (a row per router output).  wt [T, E] dense, wid [T] the identity
+    experts' share, idx / w [T, top]."""
+    ldz, lde = (z.stride(1), z.stride(0)) if by_output else (z.stride(0), z.stride(1))
+    check(core().iert_router_grouped(z.data_ptr(), ldz, lde, _ptr(correction), n_tokens, E, N, top, groups, keep,
                                      wt.data_ptr(), wid.data_ptr(), idx.data_ptr(), w.data_ptr(), stream), "router_grouped")
 
 

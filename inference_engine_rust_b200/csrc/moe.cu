@@ -62,8 +62,9 @@ __global__ void router_topk_kernel(const float* __restrict__ z, long long ldz, c
     }
 }
 
-// one warp per token; shared memory: s[N], c[N], group score [groups], flags [N] (bytes)
-__global__ void router_grouped_kernel(const float* __restrict__ z, long long ldz, const float* __restrict__ correction, int E,
+// one warp per token; shared memory: s[N], c[N], group score [groups], flags [N] (bytes).  Output e of token t is
+// z[t * ldz + e * lde]: rows of tokens (lde = 1) or rows of outputs (ldz = 1).
+__global__ void router_grouped_kernel(const float* __restrict__ z, long long ldz, long long lde, const float* __restrict__ correction, int E,
                                       int N, int top, int groups, int keep, float* __restrict__ wt, float* __restrict__ wid,
                                       int* __restrict__ idx, float* __restrict__ w) {
   extern __shared__ float rsm[];
@@ -75,10 +76,10 @@ __global__ void router_grouped_kernel(const float* __restrict__ z, long long ldz
   const int t = blockIdx.x, lane = threadIdx.x, per = N / groups;
   const float* row = z + (size_t)t * ldz;
   float m = -INFINITY;
-  for (int e = lane; e < N; e += 32) m = fmaxf(m, row[e]);
+  for (int e = lane; e < N; e += 32) m = fmaxf(m, row[e * lde]);
   m = warp_max(m);
   float den = 0.f;
-  for (int e = lane; e < N; e += 32) { const float p = expf(row[e] - m); s[e] = p; den += p; }
+  for (int e = lane; e < N; e += 32) { const float p = expf(row[e * lde] - m); s[e] = p; den += p; }
   den = warp_sum(den);
   for (int e = lane; e < N; e += 32) {
     s[e] = s[e] / den;
@@ -191,7 +192,8 @@ IERT_API int iert_router_topk(const float* z, long long ldz, const float* bias, 
   return iert_check_launch("router_topk");
 }
 
-IERT_API int iert_router_grouped(const float* z, long long ldz, const float* correction, int n_tokens, int E, int N, int top,
+// z: output e of token t at z[t * ldz + e * lde] (fp32).
+IERT_API int iert_router_grouped(const float* z, long long ldz, long long lde, const float* correction, int n_tokens, int E, int N, int top,
                                  int groups, int keep, float* wt, float* wid, int* idx, float* w, cudaStream_t stream) {
   if (n_tokens <= 0) return IERT_OK;
   if (E < 0 || N < E || N <= 0 || top <= 0 || top > MAX_TOP || groups <= 0 || N % groups || keep <= 0 || keep > groups ||
@@ -199,7 +201,7 @@ IERT_API int iert_router_grouped(const float* z, long long ldz, const float* cor
     return IERT_BAD_ARGUMENT;
   const size_t smem = (size_t)(2 * N + groups) * sizeof(float) + (size_t)N;
   if (smem > 48 * 1024) return IERT_BAD_ARGUMENT;
-  launch_dep(router_grouped_kernel, dim3(n_tokens), dim3(32), smem, stream, z, ldz, correction, E, N, top, groups, keep, wt, wid,
+  launch_dep(router_grouped_kernel, dim3(n_tokens), dim3(32), smem, stream, z, ldz, lde, correction, E, N, top, groups, keep, wt, wid,
              idx, w);
   return iert_check_launch("router_grouped");
 }

@@ -31,6 +31,11 @@ from .base import FeedForward, Runtime, StepContext, register_part
 from .linear import Linear
 
 
+# Prompts of more than this many tokens compute a grouped router's logits (at most 32 outputs) with the kernel for few
+# rows against a long matrix, the tokens being the matrix.
+SKINNY_ROUTER_MIN_TOKENS = 32
+
+
 class MoE(FeedForward):
     graph_safe = True
 
@@ -137,13 +142,24 @@ class GroupedMoE(MoE):
 
     def _route(self, xn, ctx: StepContext):
         ws, T, E, N = self.rt.workspace, ctx.n_tokens, self.experts, self.outputs
-        z = ws.take("moe.logits", (T, N), torch.float32)
-        self.router.apply(xn, z, T, ctx.stream)
         wt = ws.take("moe.weights", (T, E), torch.float32)
         wid = ws.take("moe.identity_share", (T,), torch.float32)
         idx = ws.take("moe.chosen", (T, self.top), torch.int32)
         w = ws.take("moe.chosen_weights", (T, self.top), torch.float32)
-        B.router_grouped(z, self.correction, T, E, N, self.top, self.groups, self.keep, wt, wid, idx, w, ctx.stream)
+        by_output = False
+        if (self.rt.fast and T > SKINNY_ROUTER_MIN_TOKENS and N <= 32 and isinstance(xn, torch.Tensor)
+                and xn.dtype == torch.bfloat16 and self.router.weight.dtype == torch.bfloat16):
+            # A prompt: few router outputs against many tokens.  A token tile of the tensor-core product would carry
+            # N columns and 128-token tiles alone leave most of the device idle; the kernel for few rows against a long
+            # matrix takes the router's rows as its "tokens" and the tokens as the matrix it streams, 16 tokens per
+            # CTA, and leaves the logits with a row per router output.
+            z = ws.take("moe.logits_by_output", (N, T), torch.float32)
+            by_output = B.gemm_rows(self.router.weight, xn[:T], z, N, B.GEMM_STORE, self.rt.err, ctx.stream)
+        if not by_output:
+            z = ws.take("moe.logits", (T, N), torch.float32)
+            self.router.apply(xn, z, T, ctx.stream)
+        B.router_grouped(z, self.correction, T, E, N, self.top, self.groups, self.keep, wt, wid, idx, w, ctx.stream,
+                         by_output=by_output)
         return wt, (wid if self.identity else None)
 
 

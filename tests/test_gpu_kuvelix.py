@@ -184,7 +184,11 @@ def test_router_against_the_plain_choice(N, E, top, groups, keep):
         wid = torch.full((T,), 7.0, device=DEV)
         idx = torch.zeros(T, top, dtype=torch.int32, device=DEV)
         w = torch.zeros(T, top, device=DEV)
-        b.router_grouped(zd, corr.to(DEV), T, E, N, top, groups, keep, wt, wid, idx, w, b.stream_ptr())
+        if case == 2:          # the logits stored with a row per router output
+            b.router_grouped(zd.t().contiguous(), corr.to(DEV), T, E, N, top, groups, keep, wt, wid, idx, w, b.stream_ptr(),
+                             by_output=True)
+        else:
+            b.router_grouped(zd, corr.to(DEV), T, E, N, top, groups, keep, wt, wid, idx, w, b.stream_ptr())
         ridx, rw = P.route(z, corr, top, groups, keep)
         assert torch.equal(idx.cpu().long(), ridx), f"case {case}"
         assert torch.allclose(w.cpu(), rw, atol=1e-6, rtol=1e-5)
