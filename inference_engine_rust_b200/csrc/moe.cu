@@ -25,7 +25,8 @@ __global__ void router_topk_kernel(const float* __restrict__ z, long long ldz, c
                                    int E, int top, float* __restrict__ wt, int* __restrict__ idx,
                                    float* __restrict__ w) {
   // one warp per token
-  pdl_wait();
+  pdl_launch_dependents();     // the next kernel may start its preamble now
+  pdl_wait();                  // everything below may depend on the kernel before
   const int t = blockIdx.x, lane = threadIdx.x;
   const float* row = z + (size_t)t * ldz;
   int chosen[MAX_TOP];
@@ -72,6 +73,7 @@ __global__ void router_grouped_kernel(const float* __restrict__ z, long long ldz
   float* c = rsm + N;
   float* gs = rsm + 2 * N;
   unsigned char* open = reinterpret_cast<unsigned char*>(rsm + 2 * N + groups);      // 1: may still be chosen
+  pdl_launch_dependents();     // the next kernel (the experts' product) may fetch its first weights now
   pdl_wait();
   const int t = blockIdx.x, lane = threadIdx.x, per = N / groups;
   const float* row = z + (size_t)t * ldz;
@@ -156,6 +158,7 @@ template <typename T>
 __global__ void moe_scale_kernel(T* __restrict__ act, long long ld, const float* __restrict__ wt, int E, int F,
                                  const float* __restrict__ wid, const T* __restrict__ x, long long ldx,
                                  float* __restrict__ residual, int H) {
+  pdl_launch_dependents();     // the down product may fetch its first weights now
   pdl_wait();
   const int t = blockIdx.x;
   T* row = act + (size_t)t * ld;
