@@ -449,7 +449,7 @@ def main() -> int:
                          "depth (--layers, default 8) and feed-forward size beside Mistral 7B itself, with a table of "
                          "each step's kernels against what their bytes and FLOPs allow (one JSON line)")
     ap.add_argument("--design-sizes", default="7b", choices=["7b", "12b"],
-                    help="with --design sifasun: the sizes of Mistral 7B (default) or of Mistral NeMo 12B")
+                    help="with --design sifasun or kuvelix: the sizes of Mistral 7B (default) or of Mistral NeMo 12B")
     a = ap.parse_args()
 
     if a.design is not None and a.impl != "reference":
