@@ -31,6 +31,13 @@ class KVRequest:
     head_dim: int
     window: Optional[int] = None     # None: every earlier key stays visible
     values: bool = True              # False: one row per position (keys only), e.g. a shared latent
+    chunk: Optional[int] = None      # C: a position sees only its own chunk of C positions (counted from position 0)
+
+    @property
+    def reach(self) -> Optional[int]:
+        """How many of the latest positions can still be seen (None: all of them)."""
+        both = [n for n in (self.window, self.chunk) if n]
+        return min(both) if both else None
 
 
 @dataclass(frozen=True)
@@ -58,10 +65,10 @@ class KVGroup:
         self.dtype = dtype
         self.device = device
         self.table_width = max(1, math.ceil(max_seq_len / page_tokens))
-        if req.window is None:
+        if req.reach is None:
             self.ring_pages = self.table_width
         else:
-            self.ring_pages = min(self.table_width, max(1, math.ceil(req.window / page_tokens)))
+            self.ring_pages = min(self.table_width, max(1, math.ceil(req.reach / page_tokens)))
         shape = (len(self.layers), n_pages, req.kv_heads, page_tokens, req.head_dim)
         self.k = torch.empty(shape, dtype=dtype, device=device)
         self.v = torch.empty(shape if req.values else (len(self.layers), 0) + shape[2:], dtype=dtype, device=device)
@@ -239,7 +246,7 @@ class Cache:
         return B.KvView(k=g.k[i].data_ptr(), v=g.v[i].data_ptr() if g.req.values else None, page_table=g.table.data_ptr(),
                         table_width=g.table_width, ring_pages=g.ring_pages, page_tokens=g.page_tokens,
                         n_pages=g.n_pages, kv_heads=g.req.kv_heads, head_dim=g.req.head_dim,
-                        dtype=B.dtype_code(g.dtype), window=g.req.window or 0)
+                        dtype=B.dtype_code(g.dtype), window=g.req.window or 0, chunk=g.req.chunk or 0)
 
     # ---- slots ------------------------------------------------------------------------
     def open_sequence(self) -> int:
@@ -296,8 +303,8 @@ class Cache:
         for g in self.kv_groups:
             for s in slots:
                 n = int(self.seq_lens[s])
-                if g.req.window is not None:
-                    n = min(n, g.req.window)
+                if g.req.reach is not None:
+                    n = min(n, g.req.reach)
                 total += n * g.bytes_per_token()
         return total
 

@@ -68,7 +68,7 @@ attention_decode_kernel(DecodeParams p, IertBatchView b, IertKvView c) {
     return;
   }
   const int pos = b.pos0[s] + (t - b.cu_q[s]);
-  const int j_min = c.window > 0 ? max(0, pos + 1 - c.window) : 0;
+  const int j_min = iert_first_visible(pos, c.window, c.chunk);
   // the CTA's share of the 32-key blocks that hold [j_min, pos]
   const int blk_lo = j_min / KEY_BLOCK, blk_hi = pos / KEY_BLOCK + 1;
   const int per = (blk_hi - blk_lo + p.splits - 1) / p.splits;

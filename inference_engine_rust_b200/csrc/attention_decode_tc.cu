@@ -102,7 +102,7 @@ __device__ __forceinline__ void load_page(uint8_t* tile, const __nv_bfloat16* sr
 __device__ __forceinline__ int pages_of_sequence(const IertBatchView& b, const IertKvView& c, int s) {
   if (b.slot_ids[s] < 0) return 0;
   const int pos = b.pos0[s] + (b.cu_q[s + 1] - b.cu_q[s]) - 1;
-  const int j_min = c.window > 0 ? max(0, pos + 1 - c.window) : 0;
+  const int j_min = iert_first_visible(pos, c.window, c.chunk);
   return pos / PAGE + 1 - j_min / PAGE;
 }
 
@@ -166,7 +166,7 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
     return;
   }
   const int pos = b.pos0[s] + (t - b.cu_q[s]);
-  const int j_min = c.window > 0 ? max(0, pos + 1 - c.window) : 0;
+  const int j_min = iert_first_visible(pos, c.window, c.chunk);
   const int pg_lo = j_min / PAGE, pg_hi = pos / PAGE + 1;           // logical pages [pg_lo, pg_hi)
   int n_splits = p.splits;
   if (p.target_ctas > 0 && p.splits > 1) {
@@ -464,7 +464,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     return;
   }
   const int pos = b.pos0[s] + (t - b.cu_q[s]);
-  const int j_min = c.window > 0 ? max(0, pos + 1 - c.window) : 0;
+  const int j_min = iert_first_visible(pos, c.window, c.chunk);
   const int pg_lo = j_min / PAGE, pg_hi = pos / PAGE + 1;
   int n_splits = p.splits;
   if (p.target_ctas > 0 && p.splits > 1) {
@@ -748,7 +748,7 @@ __global__ void attention_decode_tc_combine_kernel(DecodeTcParams p, IertBatchVi
   const bool live = s_ >= 0 && b.slot_ids[s_] >= 0;
   if (p.target_ctas > 0 && p.splits > 1 && live) {
     const int pos = b.pos0[s_] + (t - b.cu_q[s_]);
-    const int j_min = c.window > 0 ? max(0, pos + 1 - c.window) : 0;
+    const int j_min = iert_first_visible(pos, c.window, c.chunk);
     const int group = p.heads / c.kv_heads;
     n_splits = balanced_parts(b, c, pos / PAGE + 1 - j_min / PAGE, p.splits, p.target_ctas,
                               c.kv_heads * ((group + p.gt - 1) / p.gt), red);

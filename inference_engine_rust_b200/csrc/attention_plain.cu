@@ -4,7 +4,7 @@
 // running maximum and sum, so the memory it needs does not grow with the context.
 //
 //   scores  s_j = (q . k_j) * scale for j in [j_min, pos], causal by construction
-//   window  j_min = pos - (W - 1) (the last W keys, the current one included)
+//   window  j_min = pos - (W - 1) (the last W keys, the current one included); chunk: j_min = pos - pos % C
 //   weights softmax over the visible keys; output = sum_j p_j v_j
 //   softcap c > 0: s_j <- c tanh(s_j / c) before the softmax
 //   sink    (optional, fp32 per head): one more term exp(sink[head]) in the denominator, with no value
@@ -46,7 +46,7 @@ attention_plain_kernel(const T* __restrict__ qkv, T* __restrict__ out, IertBatch
   const int q_begin = b.cu_q[s];
   const int pos0 = b.pos0[s];
   const int pos = pos0 + (t - q_begin);
-  const int j_min = c.window > 0 ? max(0, pos - (c.window - 1)) : 0;
+  const int j_min = iert_first_visible(pos, c.window, c.chunk);
   const int kvh = head / (heads / nkv);
 
   const T* q = qkv + (size_t)t * row_elems + (size_t)head * hd;

@@ -79,7 +79,7 @@ __device__ __forceinline__ void load_tile(uint8_t* tile, const __nv_bfloat16* sr
 
 __global__ void __launch_bounds__(THREADS)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ out,
-                         IertBatchView b, int heads, int kv_heads, int window, float scale_log2e,
+                         IertBatchView b, int heads, int kv_heads, int window, int chunk, float scale_log2e,
                          const float* __restrict__ sink, float cap_k2, float cap_l2e) {
   extern __shared__ __align__(16) uint8_t smem[];
   uint8_t* q_tile = smem;
@@ -101,7 +101,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* _
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
   const int i_hi = min(len, i0 + BM) - 1;               // last valid query of the tile
-  const int j_lo = window > 0 ? max(0, i0 - (window - 1)) : 0;
+  const int j_lo = iert_first_visible(i0, window, chunk);
   const int kt_lo = j_lo / BN, kt_hi = i_hi / BN;       // key tiles to visit, inclusive
 
   load_tile<BM>(q_tile, q_src, ld, len - i0);
@@ -156,7 +156,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* _
 
     // ---- scale, mask, running softmax (base 2: scale_log2e = scale * log2(e))
     const int j0 = kt * BN;
-    const bool need_mask = (j0 + BN - 1 > i0 + warp * 16) || (window > 0 && j0 < i0 + warp * 16 + 15 - (window - 1)) ||
+    const bool need_mask = (j0 + BN - 1 > i0 + warp * 16) || j0 < iert_first_visible(i0 + warp * 16 + 15, window, chunk) ||
                            (j0 + BN > len);
     float m_new[2] = {m_row[0], m_row[1]};
 #pragma unroll
@@ -166,7 +166,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* _
         float v = cap_l2e > 0.f ? softcap_l2(sc[n][e], cap_k2, cap_l2e) : sc[n][e] * scale_log2e;
         if (need_mask) {
           const int j = j0 + n * 8 + tq * 2 + (e & 1), i = qi[e >> 1];
-          const bool vis = j <= i && j < len && (window <= 0 || j >= i - (window - 1));
+          const bool vis = j <= i && j < len && j >= iert_first_visible(i, window, chunk);
           if (!vis) v = -INFINITY;
         }
         sc[n][e] = v;
@@ -242,7 +242,7 @@ IERT_API int iert_attention_prefill_head_dim() { return HD; }
 // out: bf16 [T, heads * HEAD_DIM].  Every sequence of the step starts at position 0.
 // max_q_len: the longest sequence of the step (sizes the grid).
 IERT_API int iert_attention_prefill(const void* qkv, void* out, const IertBatchView* batch, int heads,
-                                    int kv_heads, int window, float scale, int max_q_len, const float* sink,
+                                    int kv_heads, int window, int chunk, float scale, int max_q_len, const float* sink,
                                     float softcap, cudaStream_t stream) {
   if (batch->n_tokens <= 0 || max_q_len <= 0) return IERT_OK;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || heads > 65535 || batch->n_seqs > 65535)
@@ -258,7 +258,7 @@ IERT_API int iert_attention_prefill(const void* qkv, void* out, const IertBatchV
   }
   dim3 grid((max_q_len + BM - 1) / BM, heads, batch->n_seqs);
   attention_prefill_kernel<<<grid, THREADS, smem, stream>>>(
-      (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, *batch, heads, kv_heads, window,
+      (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, *batch, heads, kv_heads, window, chunk,
       scale * 1.4426950408889634f, sink, softcap > 0.f ? 2.0f * scale * 1.4426950408889634f / softcap : 0.f,
       softcap > 0.f ? softcap * 1.4426950408889634f : 0.f);
   cudaError_t e = cudaGetLastError();

@@ -53,7 +53,7 @@ constexpr uint32_t O_COL = 128;
 
 struct PrefillTcParams {
   __nv_bfloat16* out;         // [T, heads * HD]
-  int heads, kv_heads, window;
+  int heads, kv_heads, window, chunk;
   float scale_log2e;
   float cap_k2, cap_l2e;   // a soft cap on the scores (cap_l2e > 0): see softcap_l2
   const float* sink;       // optional [heads]: a bare logit per head that adds exp(sink) to every row's denominator only
@@ -131,7 +131,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int i0 = qt * BM;
   const int kvh = head / (p.heads / p.kv_heads);
   const int i_hi = min(len, i0 + BM) - 1;
-  const int j_lo = p.window > 0 ? max(0, i0 - (p.window - 1)) : 0;
+  const int j_lo = iert_first_visible(i0, p.window, p.chunk);
   const int kt_lo = j_lo / BN, kt_hi = i_hi / BN;
   const int n_tiles = kt_hi - kt_lo + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -233,6 +233,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // ---------------- softmax: thread = query row ----------------
     const int r = warp * 32 + lane;
     const int i = i0 + r;                                    // position of this row's query
+    const int i_lo = iert_first_visible(i, p.window, p.chunk);   // the first key this row sees
     const uint32_t lane_bits = (uint32_t)(warp * 32) << 16;
     float m_used = -INFINITY, l = 0.f;
     for (int it = 0; ok && it < n_tiles; ++it) {
@@ -256,12 +257,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       // Scores stay raw; the scale (> 0) is folded into the exponent: p = 2^(s * scale - m).
       // A tile that every row sees entirely (the common case) takes the path without masks.
-      const bool need_mask = (j0 + BN - 1 > i0) || (p.window > 0 && j0 < i0 + BM - 1 - (p.window - 1)) || (j0 + BN > len);
+      const bool need_mask = (j0 + BN - 1 > i0) || j0 < iert_first_visible(i0 + BM - 1, p.window, p.chunk) || (j0 + BN > len);
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < BN; ++c) {
           const int j = j0 + c;
-          const bool vis = j <= i && j < len && (p.window <= 0 || j >= i - (p.window - 1));
+          const bool vis = j <= i && j < len && j >= i_lo;
           if (!vis) sc[c] = -INFINITY;
         }
       }
@@ -367,7 +368,7 @@ IERT_API int iert_attention_prefill_tc_available() { return 1; }
 // Same contract as iert_attention_prefill; additionally qkv must be 16-byte aligned.  Returns
 // IERT_BAD_ARGUMENT (nothing launched) when the tensor map cannot be made.
 IERT_API int iert_attention_prefill_tc(const void* qkv, void* out, const IertBatchView* batch, int heads,
-                                       int kv_heads, int window, float scale, int max_q_len, int* err,
+                                       int kv_heads, int window, int chunk, float scale, int max_q_len, int* err,
                                        const float* sink, float softcap, cudaStream_t stream) {
   if (batch->n_tokens <= 0 || max_q_len <= 0) return IERT_OK;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || (max_q_len + BM - 1) / BM > 65535 || batch->n_seqs > 65535 ||
@@ -380,7 +381,7 @@ IERT_API int iert_attention_prefill_tc(const void* qkv, void* out, const IertBat
     return IERT_BAD_ARGUMENT;
   PrefillTcParams p;
   p.out = (__nv_bfloat16*)out;
-  p.heads = heads; p.kv_heads = kv_heads; p.window = window;
+  p.heads = heads; p.kv_heads = kv_heads; p.window = window; p.chunk = chunk;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.sink = sink;
   p.cap_k2 = softcap > 0.f ? 2.0f * scale * 1.4426950408889634f / softcap : 0.f;
@@ -403,7 +404,7 @@ IERT_API int iert_attention_prefill_tc(const void* qkv, void* out, const IertBat
 #else   // other head sizes: the mma.sync kernel serves them
 
 IERT_API int iert_attention_prefill_tc_available() { return 0; }
-IERT_API int iert_attention_prefill_tc(const void*, void*, const IertBatchView*, int, int, int, float, int, int*, const float*,
+IERT_API int iert_attention_prefill_tc(const void*, void*, const IertBatchView*, int, int, int, int, float, int, int*, const float*,
                                        float, cudaStream_t) {
   return IERT_BAD_ARGUMENT;
 }

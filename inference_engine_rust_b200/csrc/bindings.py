@@ -35,7 +35,7 @@ class KvView(Structure):
     _fields_ = [("k", c_void_p), ("v", c_void_p), ("page_table", c_void_p),
                 ("table_width", c_int), ("ring_pages", c_int), ("page_tokens", c_int),
                 ("n_pages", c_int), ("kv_heads", c_int), ("head_dim", c_int),
-                ("dtype", c_int), ("window", c_int)]
+                ("dtype", c_int), ("window", c_int), ("chunk", c_int)]
 
 
 class BatchView(Structure):
@@ -140,12 +140,19 @@ def _declare(lib) -> None:
         "iert_latent_norm_store": [P, LL, c_int, c_int, P, P, c_float, P, P, c_int, POINTER(BatchView), POINTER(KvView),
                                    c_int, P, S],
         "iert_latent_attention_prompt": [P, LL, P, c_int, POINTER(BatchView), c_int, c_int, c_int, c_float, P, S],
-        "iert_latent_attention_decode": [P, LL, P, P, P, c_int, POINTER(BatchView), POINTER(KvView), c_int, c_int, c_int,
-                                         c_float, P, P, S],
+        "iert_latent_attention_decode": [P, LL, P, P, P, c_int, POINTER(BatchView), POINTER(KvView), c_int, c_int, c_int, c_int,
+                                         c_float, P, P, P, S],
+        "iert_latent_prep": [P, LL, c_int, c_int, c_int, c_int, P, c_float, P, c_int, c_int, c_float, P, P, LL, c_int, P, c_int,
+                             POINTER(BatchView), POINTER(KvView), c_int, P, S],
+        "iert_head_gate_mul": [P, c_int, P, c_int, c_int, P, c_int, c_int, S],
+        "iert_token_shift": [P, c_int, LL, P, LL, LL, P, c_int, c_int, P, POINTER(BatchView), S],
+        "iert_wkv_decay": [P, LL, c_int, P, P, c_int, P, P, c_int, LL, c_int, P, LL, LL, POINTER(BatchView), S],
+        "iert_wkv_finish": [P, P, LL, P, c_float, c_float, P, c_int, c_int, c_int, c_int, S],
         "iert_latent_decode_tc_plan": [c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)],
         "iert_router_topk": [P, LL, P, c_int, c_int, c_int, P, P, P, S],
         "iert_moe_scale": [P, c_int, LL, P, c_int, c_int, c_int, P, P, LL, P, c_int, S],
-        "iert_router_grouped": [P, LL, LL, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P, P, P, S],
+        "iert_router_grouped": [P, LL, LL, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                                P, P, P, P, S],
         "iert_qkv_prep": [P, LL, P, P, c_int, POINTER(BatchView), POINTER(KvView), c_int, c_int, c_int, P, c_int, c_int, P, P,
                           c_float, c_int, P, S],
         "iert_gate_mul": [P, P, LL, P, c_int, c_int, c_int, c_int, c_int, S],
@@ -166,7 +173,7 @@ def _declare(lib) -> None:
                                        c_int, c_int, P, S]
     lib.iert_gemm_tc_gated.restype = c_int
     lib.iert_gemm_rows.argtypes = [P, c_longlong, P, c_longlong, P, c_int, c_longlong, c_int, c_int, c_int, c_int,
-                                   POINTER(RowScale), POINTER(NormAhead), c_int, P, S]
+                                   POINTER(RowScale), POINTER(NormAhead), c_int, c_int, P, S]
     lib.iert_gemm_rows.restype = c_int
     lib.iert_gemm_tc_scaled.argtypes = [P, c_longlong, P, c_longlong, P, c_int, c_longlong, c_int, c_int, c_int, c_int,
                                         P, c_longlong, P, c_int, POINTER(RowScale), POINTER(NormAhead), c_int, c_int, P, S]
@@ -384,17 +391,18 @@ def gemm_tc(x, w, out, M: int, mode: int, err, stream, force_bt: int = 0, force_
 
 
 def gemm_rows(x, w, out, M: int, mode: int, err, stream, scale: Optional[RowScale] = None,
-              ahead: Optional[NormAhead] = None, force_stages: int = 0) -> bool:
+              ahead: Optional[NormAhead] = None, force_stages: int = 0, w_dynamic: bool = False) -> bool:
     """out[:M] (=|+=) x[:M] @ w.T for one-token steps (M <= 32, bf16 operands): 16 weight rows per
     CTA over all of k, no split-K.  `scale`: x is the first half of an RMSNorm and the outputs
     are multiplied by the rows' 1 / rms; `ahead` (with a residual add): the first half of the
-    next norm is written beside the new rows and `ahead.parts` is set.  Returns False, having
+    next norm is written beside the new rows and `ahead.parts` is set.  `w_dynamic`: `w` is no stored weight but rows
+    the kernel in front wrote, so none of it is fetched ahead of the wait for that kernel.  Returns False, having
     launched nothing, when the operands do not meet the kernel's rules."""
     N, K = w.shape
     status = core().iert_gemm_rows(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
                                    dtype_code(out.dtype), out.stride(0), M, N, K, mode,
                                    byref(scale) if scale is not None else None,
-                                   byref(ahead) if ahead is not None else None, force_stages,
+                                   byref(ahead) if ahead is not None else None, force_stages, 1 if w_dynamic else 0,
                                    err.data_ptr(), stream)
     if status == 1:
         return False
@@ -462,7 +470,7 @@ def _attention_lib(head_dim: int):
     lib = _attn_libs.get(head_dim)
     if lib is None:
         lib = build.load_library(*build.attention_library(head_dim))
-        lib.iert_attention_prefill.argtypes = [c_void_p, c_void_p, POINTER(BatchView), c_int, c_int, c_int,
+        lib.iert_attention_prefill.argtypes = [c_void_p, c_void_p, POINTER(BatchView), c_int, c_int, c_int, c_int,
                                                c_float, c_int, c_void_p, c_float, c_void_p]
         lib.iert_attention_prefill.restype = c_int
         lib.iert_attention_decode_tc.argtypes = [c_void_p, c_void_p, POINTER(BatchView), POINTER(KvView), c_int,
@@ -472,7 +480,7 @@ def _attention_lib(head_dim: int):
                                                       c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                                       c_void_p, c_void_p]
         lib.iert_attention_decode_tc_rope.restype = c_int
-        lib.iert_attention_prefill_tc.argtypes = [c_void_p, c_void_p, POINTER(BatchView), c_int, c_int, c_int,
+        lib.iert_attention_prefill_tc.argtypes = [c_void_p, c_void_p, POINTER(BatchView), c_int, c_int, c_int, c_int,
                                                   c_float, c_int, c_void_p, c_void_p, c_float, c_void_p]
         lib.iert_attention_prefill_tc.restype = c_int
         lib.iert_attention_prefill_tc_available.restype = c_int
@@ -485,8 +493,9 @@ def _attention_lib(head_dim: int):
 
 def attention_prefill(qkv, out, batch: BatchView, heads: int, kv_heads: int, head_dim: int, window: int,
                       scale: float, max_q_len: int, stream, err=None, legacy: bool = False, sink=None,
-                      softcap: float = 0.0) -> bool:
-    """Flash prompt attention (bf16) over the step's own keys and values.  Head sizes 64 and
+                      softcap: float = 0.0, chunk: int = 0) -> bool:
+    """Flash prompt attention (bf16) over the step's own keys and values (`window` W > 0: the last W keys; `chunk`
+    C > 0: the keys of the query's own chunk of C positions).  Head sizes 64 and
     128 run on tcgen05 with the scores and the output in tensor memory (unless `legacy`); other
     multiples of 16 up to 256 run the mma.sync kernel.  The library is compiled per head size
     the first time it is needed; anything else returns False and nothing is launched.  `sink` (fp32
@@ -499,7 +508,7 @@ def attention_prefill(qkv, out, batch: BatchView, heads: int, kv_heads: int, hea
     if not legacy and err is not None and lib.iert_attention_prefill_tc_available() \
             and os.environ.get("IERT_ATTN_TC", "1") != "0":
         status = lib.iert_attention_prefill_tc(qkv.data_ptr(), out.data_ptr(), byref(batch), heads, kv_heads,
-                                               window, scale, max_q_len, err.data_ptr(),
+                                               window, chunk, scale, max_q_len, err.data_ptr(),
                                                sink.data_ptr() if sink is not None else None, softcap, stream)
         if status == 0:
             launch_count += 1
@@ -507,7 +516,7 @@ def attention_prefill(qkv, out, batch: BatchView, heads: int, kv_heads: int, hea
         if status != 1:
             raise KernelError("attention_prefill_tc: the launch failed")
     status = lib.iert_attention_prefill(qkv.data_ptr(), out.data_ptr(), byref(batch), heads, kv_heads,
-                                        window, scale, max_q_len, sink.data_ptr() if sink is not None else None, softcap,
+                                        window, chunk, scale, max_q_len, sink.data_ptr() if sink is not None else None, softcap,
                                         stream)
     if status == 1:
         return False
@@ -647,6 +656,8 @@ def _recurrent_lib(dim: int):
         lib.iert_mlstm_recur.argtypes = [P, c_int, LL, P, LL, P, P, c_float, P, LL, LL, LL, LL, P, P, c_int, c_int,
                                          POINTER(BatchView), P]
         lib.iert_mlstm_recur.restype = c_int
+        lib.iert_wkv_recur.argtypes = [P, LL, P, P, P, LL, LL, P, c_int, c_int, POINTER(BatchView), P]
+        lib.iert_wkv_recur.restype = c_int
         if os.environ.get("IERT_PDL", "1") == "0":
             lib.iert_set_pdl(0)
         _recurrent_libs[dim] = lib
@@ -679,6 +690,35 @@ def mlstm_recur(proj, gates, bi, bf, cap: float, state, s_off: int, n_off: int, 
                                                   byref(batch), stream), "mlstm_recur", 2)
 
 
+def token_shift(h, state, prev_off: int, mu, mixed, batch: BatchView, stream) -> None:
+    """mixed[m, t] = h[t] + (h[t-1] - h[t]) * mu[m]; in front of a sequence's first token stands the row that
+    `state` [slots, floats] keeps at `prev_off`."""
+    n_mix, width = mu.shape
+    check(core().iert_token_shift(h.data_ptr(), dtype_code(h.dtype), h.stride(0), state.data_ptr(), state.stride(0), prev_off,
+                                  mu.data_ptr(), n_mix, width, mixed.data_ptr(), byref(batch), stream), "token_shift")
+
+
+def wkv_decay(z, L: int, w2t, w0, decay, h, state, prev_off: int, batch: BatchView, stream) -> None:
+    """decay[t, c] = exp(-exp(w0[c] + sum_l w2t[l, c] tanh(z[t, l]))) (fp32); also leaves every sequence's last row
+    of `h` in `state` at `prev_off`."""
+    check(core().iert_wkv_decay(z.data_ptr(), z.stride(0), L, w2t.data_ptr(), w0.data_ptr(), w0.numel(), decay.data_ptr(),
+                                h.data_ptr(), dtype_code(h.dtype), h.stride(0), h.shape[-1], state.data_ptr(), state.stride(0),
+                                prev_off, byref(batch), stream), "wkv_decay")
+
+
+def wkv_recur(x, decay, u, state, s_off: int, o, D: int, H: int, V: int, batch: BatchView, stream) -> None:
+    """o_t = (S + diag(u) k_t v_t^T)^T r_t; S <- diag(w_t) S + k_t v_t^T over the step's tokens, from the fp32
+    projections x = [r | k | v | ...] and the decays w; S [H, D, V] per slot in `state` at `s_off`."""
+    _check_lib(_recurrent_lib(D).iert_wkv_recur(x.data_ptr(), x.stride(0), decay.data_ptr(), u.data_ptr(), state.data_ptr(),
+                                                state.stride(0), s_off, o.data_ptr(), H, V, byref(batch), stream), "wkv_recur")
+
+
+def wkv_finish(o, gate, w, eps: float, out_scale: float, out, n_tokens: int, H: int, V: int, stream) -> None:
+    """out = o / rms(o) per head * w * silu(gate) * out_scale (gate: fp32 [T, >= H*V])."""
+    check(core().iert_wkv_finish(o.data_ptr(), gate.data_ptr(), gate.stride(0), w.data_ptr(), eps, out_scale, out.data_ptr(),
+                                 dtype_code(out.dtype), n_tokens, H, V, stream), "wkv_finish")
+
+
 # ---------------------------------------------------------------------------------------
 # latent attention, routing
 
@@ -696,10 +736,30 @@ def latent_attention_prompt(qkv, out, batch: BatchView, H: int, D: int, V: int, 
 
 
 def latent_attention_decode(q, w_uk, w_uv, out, batch: BatchView, kv: KvView, H: int, D: int, V: int, scale: float, sink,
-                            err, stream) -> None:
+                            err, stream, rot_dim: int = 0, gate=None) -> None:
+    """`rot_dim` R: a query head is [D unrotated | R rotated] and a cached row [latent | R rotated key numbers];
+    `gate` (fp32 [T, H], optional) multiplies each head's result."""
     check(core().iert_latent_attention_decode(q.data_ptr(), q.stride(0), w_uk.data_ptr(), w_uv.data_ptr(), out.data_ptr(),
-                                              dtype_code(q.dtype), byref(batch), byref(kv), H, D, V, scale, _ptr(sink),
-                                              err.data_ptr(), stream), "latent_attention_decode")
+                                              dtype_code(q.dtype), byref(batch), byref(kv), H, D, rot_dim, V, scale, _ptr(sink),
+                                              _ptr(gate), err.data_ptr(), stream), "latent_attention_decode")
+
+
+def latent_prep(x, H: int, D: int, R: int, rank: int, wkv, eps: float, inv_freq, pairing: int, out_scale: float, c_ext, q_out,
+                q_head: int, gate_out, batch: BatchView, kv: KvView, store: bool, err, stream) -> None:
+    """From the fp32 projection rows x = [q: H x (D | R) | latent: rank | rotated key part: R | gate logits: H (if
+    `gate_out`)] to the normed latent and rotated key part `c_ext` [T, rank + R] (also the cache row, with `store`), the
+    queries `q_out` [T, H, q_head] (rotated part turned, zeros beyond D + R) and `gate_out` = sigmoid(logit) * out_scale."""
+    check(core().iert_latent_prep(x.data_ptr(), x.stride(0), H, D, R, rank, wkv.data_ptr(), eps, _ptr(inv_freq), pairing,
+                                  1 if gate_out is not None else 0, out_scale, c_ext.data_ptr(), q_out.data_ptr(), q_out.stride(0),
+                                  q_head,
+                                  _ptr(gate_out), dtype_code(c_ext.dtype), byref(batch), byref(kv), 1 if store else 0,
+                                  err.data_ptr(), stream), "latent_prep")
+
+
+def head_gate_mul(attn, head: int, out, V: int, H: int, gate, n_tokens: int, stream) -> None:
+    """out[t, h, :V] = attn[t, h, :V] * gate[t, h] for heads stored `head` numbers apart (gate None: a plain copy)."""
+    check(core().iert_head_gate_mul(attn.data_ptr(), head, out.data_ptr(), V, H, _ptr(gate), dtype_code(attn.dtype), n_tokens,
+                                    stream), "head_gate_mul")
 
 
 def latent_decode_tc_plan(n_seqs: int, H: int, table_width: int):
@@ -710,7 +770,8 @@ def latent_decode_tc_plan(n_seqs: int, H: int, table_width: int):
 
 
 def latent_attention_decode_tc(q, w_uk, w_uv, out, batch: BatchView, kv: KvView, H: int, D: int, V: int, scale: float, sink,
-                               hpad: int, splits: int, qa, part_m, part_l, part_acc, err, stream) -> bool:
+                               hpad: int, splits: int, qa, part_m, part_l, part_acc, err, stream, rot_dim: int = 0,
+                               gate=None) -> bool:
     """One-token latent attention on the tensor cores (bf16, rank a multiple of 32 up to 512, pages of 64):
     the absorbed queries, the split attention over the cached latents, the merge with the sink and W_uv.
     Returns False, having launched nothing, for sizes it does not take."""
@@ -718,11 +779,12 @@ def latent_attention_decode_tc(q, w_uk, w_uv, out, batch: BatchView, kv: KvView,
     fn = lib.iert_latent_attention_decode_tc
     if not getattr(fn, "_declared", False):
         fn.argtypes = [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, POINTER(BatchView), POINTER(KvView), c_int, c_int,
-                       c_int, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+                       c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_void_p]
         fn.restype = c_int
         fn._declared = True
-    status = fn(q.data_ptr(), q.stride(0), w_uk.data_ptr(), w_uv.data_ptr(), out.data_ptr(), byref(batch), byref(kv), H, D, V,
-                scale, _ptr(sink), hpad, splits, qa.data_ptr(), part_m.data_ptr(), part_l.data_ptr(), part_acc.data_ptr(),
+    status = fn(q.data_ptr(), q.stride(0), w_uk.data_ptr(), w_uv.data_ptr(), out.data_ptr(), byref(batch), byref(kv), H, D,
+                rot_dim, V, scale, _ptr(sink), _ptr(gate), hpad, splits, qa.data_ptr(), part_m.data_ptr(), part_l.data_ptr(), part_acc.data_ptr(),
                 err.data_ptr(), stream)
     if status == 1:
         return False
@@ -737,14 +799,21 @@ def router_topk(z, bias, n_tokens: int, E: int, top: int, wt, idx, w, stream) ->
                                   w.data_ptr(), stream), "router_topk")
 
 
+ROUTER_SCORES = {"softmax": 0, "sigmoid": 1}
+ROUTER_GROUP_SCORES = {"max": 0, "top2_sum": 1}
+
+
 def router_grouped(z, correction, n_tokens: int, E: int, N: int, top: int, groups: int, keep: int, wt, wid, idx, w,
-                   stream, by_output: bool = False) -> None:
-    """Scores = softmax over all N router outputs (the last N - E stand for experts that return their input); choice on
-    score + correction inside the `keep` best of `groups` runs of neighbours; weights = chosen scores over their sum.
-    z: fp32 [T, N], or with `by_output` [N, T] (a row per router output).  wt [T, E] dense, wid [T] the identity
-    experts' share, idx / w [T, top]."""
+                   stream, by_output: bool = False, score: str = "softmax", group_score: str = "max",
+                   weight_eps: float = 1e-20, weight_scale: float = 1.0) -> None:
+    """Scores = softmax over all N router outputs, or each output's sigmoid (the last N - E stand for experts that return
+    their input); choice on score + correction inside the `keep` best of `groups` runs of neighbours (a run's score: its
+    best choice score, or the sum of its two best); weights = chosen scores over (their sum + weight_eps), times
+    weight_scale.  z: fp32 [T, N], or with `by_output` [N, T] (a row per router output).  wt [T, E] dense, wid [T] the
+    identity experts' share, idx / w [T, top]."""
     ldz, lde = (z.stride(1), z.stride(0)) if by_output else (z.stride(0), z.stride(1))
     check(core().iert_router_grouped(z.data_ptr(), ldz, lde, _ptr(correction), n_tokens, E, N, top, groups, keep,
+                                     ROUTER_SCORES[score], ROUTER_GROUP_SCORES[group_score], weight_eps, weight_scale,
                                      wt.data_ptr(), wid.data_ptr(), idx.data_ptr(), w.data_ptr(), stream), "router_grouped")
 
 

@@ -35,6 +35,8 @@ enum : int { IERT_PAIR_HALF = 0, IERT_PAIR_INTERLEAVED = 1 };
 //                 (b % ring_pages) of its row (ring_pages >= table_width means "no ring")
 //   window      : 0 = every earlier key is visible; W > 0 = the last W keys, the current
 //                 one included
+//   chunk       : C > 0 = only the keys of the position's own chunk of C positions (chunks are counted
+//                 from position 0 of the sequence); combines with a window (the later lower bound wins)
 struct IertKvView {
   void* k;
   void* v;
@@ -47,7 +49,15 @@ struct IertKvView {
   int head_dim;
   int dtype;
   int window;
+  int chunk;
 };
+
+// The first position that position `pos` sees under a window and a chunk rule (either may be 0 = none).
+__host__ __device__ __forceinline__ int iert_first_visible(int pos, int window, int chunk) {
+  int lo = window > 0 ? pos + 1 - window : 0;
+  if (chunk > 0) { const int c = pos - pos % chunk; lo = lo > c ? lo : c; }
+  return lo > 0 ? lo : 0;
+}
 
 // The sequences of one step.  All arrays live on the device.
 //   cu_q[n_seqs+1] : prefix sums of the tokens each sequence brings

@@ -72,6 +72,7 @@ struct RowsParams {
   IertRowScale scale;                     // scale.sumsq != null: the outputs are multiplied by the rows' 1 / rms
   IertNormAhead ahead;                    // ahead.scaled_out != null (residual add): the next norm's first half
   int trace_seq;
+  int w_dynamic;                          // the matrix operand was written by the kernel in front: nothing is fetched before the wait
 };
 
 __device__ __forceinline__ void ldsm4(uint32_t (&r)[4], const void* p) {
@@ -133,6 +134,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     if (lane == 0) {
       bool ok = true, dep_ready = false;
       int armed = 0;                                        // ring uses asked for so far
+      if (p.w_dynamic) { pdl_wait(); dep_ready = true; }   // no operand is a stored weight: both come after the wait
       // the weights / the tokens of ring use s into slot st (k-blocks beyond K read as zeros)
       auto load_w = [&](int s, int st) {
         uint8_t* base = smem + (size_t)st * STAGE_BYTES;
@@ -330,11 +332,13 @@ IERT_API int iert_gemm_rows_trace_read(unsigned long long* stamps, int* meta) {
 // IERT_BAD_ARGUMENT is returned and nothing is launched.  force_stages: 0 = choose.
 //   scale (optional)  the rows of x are the first half of an RMSNorm (IertNormAhead of the kernel that
 //                     wrote them): the outputs are multiplied by each row's 1 / rms (see common.cuh).
+//   w_dynamic         w is no stored weight but rows that the kernel in front wrote (a few stored rows against many
+//                     tokens, the tokens as the streamed matrix): it is not fetched ahead of the dependency wait.
 //   ahead (optional; mode 1)  the first half of the NEXT norm over the new rows of `out`: ahead->parts
 //                     is set to the number of partial sums per row written (one per CTA).
 IERT_API int iert_gemm_rows(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
                             long long ldo, int M, int N, int K, int mode, const IertRowScale* scale,
-                            IertNormAhead* ahead, int force_stages, int* err, cudaStream_t stream) {
+                            IertNormAhead* ahead, int force_stages, int w_dynamic, int* err, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return IERT_OK;
   if (M > 32 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
     return IERT_BAD_ARGUMENT;
@@ -348,7 +352,7 @@ IERT_API int iert_gemm_rows(const void* x, long long ldx, const void* w, long lo
   const int nt = M <= 8 ? 1 : M <= 16 ? 2 : 4;
   RowsParams p;
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.mode = mode;
-  p.M = M; p.N = N; p.K = K; p.err = err;
+  p.M = M; p.N = N; p.K = K; p.err = err; p.w_dynamic = w_dynamic;
   p.scale = IertRowScale{nullptr, 0, 0, 0.f};
   if (scale) p.scale = *scale;
   p.ahead = IertNormAhead{nullptr, 0, nullptr, 0, nullptr, 0};

@@ -12,7 +12,10 @@
 //   keys and values, packed per token as q [H*D] | k [H*D] | v [H*V] (D and V may differ).
 // latent_attention_decode: one token per sequence over the cached latents, in the absorbed form:
 //   qa = W_uk[h]^T q  (rank numbers), s_j = (qa . c_j) * scale, l = sum_j p_j c_j, o = W_uv[h] l.
-//   Nothing is expanded per cached position.
+//   Nothing is expanded per cached position.  With a rotated part of R numbers a cached row is [c_j | r_j] (r_j: one
+//   rotated key part shared by all heads), a query head is [unrotated D | rotated R], and s_j = (qa . c_j + q_rot . r_j)
+//   * scale; the weighted sum still runs over the latents alone.  `gate` (fp32 [T, H], optional) multiplies head h's result.
+// latent_prep / head_gate_mul: the preparation of that variant's rows and the gate on a prompt's result (below).
 // All arithmetic is fp32; one block per (token, head); keys are visited in chunks with a running
 // maximum and sum, so the memory needed does not grow with the context.
 #include "common.cuh"
@@ -130,14 +133,14 @@ template <typename T>
 __global__ void __launch_bounds__(THREADS)
 latent_attention_decode_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ w_uk,
                                const T* __restrict__ w_uv, T* __restrict__ out, IertBatchView b, IertKvView kv,
-                               int H, int D, int V, float scale, const float* __restrict__ sink,
-                               int* __restrict__ err) {
+                               int H, int D, int R, int V, float scale, const float* __restrict__ sink,
+                               const float* __restrict__ gate, int* __restrict__ err) {
   extern __shared__ float smem[];
-  const int rank = kv.head_dim;
-  float* qa = smem;                   // [rank]: the query in the latent's coordinates
-  float* lat = qa + rank;             // [rank]: the weighted sum of latents
-  float* q_s = lat + rank;            // [D]
-  float* p_s = q_s + D;               // [THREADS]
+  const int width = kv.head_dim, rank = width - R;   // a cached row: the latent [rank] | the shared rotated key part [R]
+  float* qa = smem;                   // [width]: the query in the latent's coordinates | its rotated part
+  float* lat = qa + width;            // [rank]: the weighted sum of latents
+  float* q_s = lat + rank;            // [D + R]
+  float* p_s = q_s + D + R;           // [THREADS]
   float* scratch = p_s + THREADS;     // [33]
   pdl_wait();
   const int t = blockIdx.x, head = blockIdx.y;
@@ -149,7 +152,7 @@ latent_attention_decode_kernel(const T* __restrict__ q, long long ldq, const T* 
     return;
   }
   const int pos = b.pos0[s] + (t - b.cu_q[s]);
-  for (int d = threadIdx.x; d < D; d += THREADS) q_s[d] = to_f32(q[(size_t)t * ldq + (size_t)head * D + d]);
+  for (int d = threadIdx.x; d < D + R; d += THREADS) q_s[d] = to_f32(q[(size_t)t * ldq + (size_t)head * (D + R) + d]);
   __syncthreads();
   for (int r = threadIdx.x; r < rank; r += THREADS) {
     const T* w = w_uk + (size_t)head * D * rank + r;
@@ -157,6 +160,7 @@ latent_attention_decode_kernel(const T* __restrict__ q, long long ldq, const T* 
     for (int d = 0; d < D; ++d) a = fmaf(q_s[d], to_f32(w[(size_t)d * rank]), a);
     qa[r] = a;
   }
+  for (int i = threadIdx.x; i < R; i += THREADS) qa[rank + i] = q_s[D + i];
   __syncthreads();
   const float snk = sink ? sink[head] : -INFINITY;
   float m = snk, l = sink ? 1.f : 0.f;
@@ -172,7 +176,7 @@ latent_attention_decode_kernel(const T* __restrict__ q, long long ldq, const T* 
       if (off >= 0) {
         const T* c = cache + off;
         float dot = 0.f;
-        for (int r = 0; r < rank; ++r) dot = fmaf(qa[r], to_f32(c[r]), dot);
+        for (int r = 0; r < width; ++r) dot = fmaf(qa[r], to_f32(c[r]), dot);
         sc = dot * scale;
       }
     }
@@ -207,7 +211,86 @@ latent_attention_decode_kernel(const T* __restrict__ q, long long ldq, const T* 
     float a = 0.f;
     for (int r = lane; r < rank; r += 32) a = fmaf(to_f32(w[r]), lat[r], a);
     a = warp_sum(a);
-    if (lane == 0) o[e] = from_f32<T>(a);
+    if (lane == 0) o[e] = from_f32<T>(gate ? a * gate[(size_t)t * H + head] : a);
+  }
+}
+
+// The step's rows of latent attention with a rotated part, from one fp32 projection row per token
+//   x = [ q: H heads of (D unrotated | R rotated) | down: rank latent numbers | R rotated key numbers | H gate logits ]
+// to what the attention kernels read:
+//   c_ext [T, rank + R]   RMS-normed latent (plain weight, eps inside the root) | rotated key part; also the cache row
+//   q_out [T, H, q_head]  per head (D unrotated | R rotated | zeros up to q_head)
+//   gate_out [T, H]       sigmoid(gate logit) * out_scale  (fp32), if the layer has a gate
+// Angles are position * inv_freq[i] in fp32 with the precise sine and cosine; pairs are neighbours (2i, 2i+1) or
+// halves (i, i + R/2).  One block per token; all arithmetic fp32, one rounding at the store.
+template <typename T>
+__global__ void latent_prep_kernel(const float* __restrict__ x, long long ldx, int H, int D, int R, int rank,
+                                   const float* __restrict__ wkv, float eps, const float* __restrict__ inv_freq, int pairing,
+                                   int has_gate, float out_scale, T* __restrict__ c_ext, T* __restrict__ q_out, long long ldq,
+                                   int q_head, float* __restrict__ gate_out, IertBatchView b, IertKvView kv, int store,
+                                   int* __restrict__ err) {
+  __shared__ float scratch[33];
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int s = sequence_of_token(b, t);
+  const int slot = s >= 0 ? b.slot_ids[s] : -1;
+  T* qrow = q_out + (size_t)t * ldq;
+  if (slot < 0) {                       // padding: rows of zeros, nothing stored
+    for (int i = threadIdx.x; i < H * q_head; i += blockDim.x) qrow[i] = from_f32<T>(0.f);
+    for (int i = threadIdx.x; i < rank + R; i += blockDim.x) c_ext[(size_t)t * (rank + R) + i] = from_f32<T>(0.f);
+    if (has_gate) for (int i = threadIdx.x; i < H; i += blockDim.x) gate_out[(size_t)t * H + i] = 0.f;
+    return;
+  }
+  const int pos = b.pos0[s] + (t - b.cu_q[s]);
+  const float* row = x + (size_t)t * ldx;
+  const float* down = row + (size_t)H * (D + R);
+  const float* glog = down + rank + R;
+  const int half = R / 2;
+  // the rotated partner and sign of element i of a rotated part: out = v[i] cos - v[partner] sin for the first of a pair
+  auto rotated = [&](const float* v, int i) -> float {
+    int k, first;
+    if (pairing == IERT_PAIR_INTERLEAVED) { k = i >> 1; first = !(i & 1); }
+    else { k = i < half ? i : i - half; first = i < half; }
+    const int other = pairing == IERT_PAIR_INTERLEAVED ? (i ^ 1) : (first ? i + half : i - half);
+    float sn, cs;
+    sincosf((float)pos * inv_freq[k], &sn, &cs);
+    return first ? v[i] * cs - v[other] * sn : v[i] * cs + v[other] * sn;
+  };
+  for (int i = threadIdx.x; i < H * q_head; i += blockDim.x) {
+    const int h = i / q_head, d = i - h * q_head;
+    const float* qh = row + (size_t)h * (D + R);
+    float v = 0.f;
+    if (d < D) v = qh[d];
+    else if (d < D + R) v = rotated(qh + D, d - D);
+    qrow[i] = from_f32<T>(v);
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) ss = fmaf(down[i], down[i], ss);
+  const float rk = 1.0f / sqrtf(block_sum(ss, scratch) / (float)rank + eps);
+  T* dst = nullptr;
+  if (store && pos >= b.pos0[s] + (b.cu_q[s + 1] - b.cu_q[s]) - kv.ring_pages * kv.page_tokens) {
+    const long long off = kv_row_offset(kv, slot, pos, 0, err);
+    if (off >= 0) dst = (T*)kv.k + off;
+  }
+  for (int i = threadIdx.x; i < rank + R; i += blockDim.x) {
+    const T v = from_f32<T>(i < rank ? down[i] * rk * wkv[i] : rotated(down + rank, i - rank));
+    c_ext[(size_t)t * (rank + R) + i] = v;
+    if (dst) dst[i] = v;
+  }
+  if (has_gate)
+    for (int i = threadIdx.x; i < H; i += blockDim.x) gate_out[(size_t)t * H + i] = out_scale / (1.0f + expf(-glog[i]));
+}
+
+// out[t, h, :V] = attn[t, h, :V] * gate[t, h]: drops the padding of heads of `head` numbers and applies the gate.
+template <typename T>
+__global__ void head_gate_mul_kernel(const T* __restrict__ attn, int head, T* __restrict__ out, int V, int H,
+                                     const float* __restrict__ gate) {
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < H * V; i += blockDim.x) {
+    const int h = i / V, e = i - h * V;
+    const float g = gate ? gate[(size_t)t * H + h] : 1.f;
+    out[(size_t)t * H * V + i] = from_f32<T>(to_f32(attn[((size_t)t * H + h) * head + e]) * g);
   }
 }
 
@@ -253,21 +336,59 @@ IERT_API int iert_latent_attention_prompt(const void* qkv, long long ld, void* o
 // the cache view holds the latents (k only).  out [T, H*V].
 IERT_API int iert_latent_attention_decode(const void* q, long long ldq, const void* w_uk, const void* w_uv, void* out,
                                           int dtype, const IertBatchView* batch, const IertKvView* kv, int H, int D,
-                                          int V, float scale, const float* sink, int* err, cudaStream_t stream) {
+                                          int R, int V, float scale, const float* sink, const float* gate, int* err,
+                                          cudaStream_t stream) {
   if (batch->n_tokens <= 0) return IERT_OK;
-  const int rank = kv->head_dim;
-  if (H <= 0 || H > 65535 || D <= 0 || V <= 0 || rank <= 0 || rank > THREADS * MAX_PER_THREAD || kv->kv_heads != 1 ||
-      kv->dtype != dtype || 2 * rank + D > 10000)
+  const int rank = kv->head_dim - R;
+  if (H <= 0 || H > 65535 || D <= 0 || R < 0 || V <= 0 || rank <= 0 || rank > THREADS * MAX_PER_THREAD || kv->kv_heads != 1 ||
+      kv->dtype != dtype || 2 * rank + D + 2 * R > 10000)
     return IERT_BAD_ARGUMENT;
   dim3 grid(batch->n_tokens, H);
-  const size_t smem = (size_t)(2 * rank + D + THREADS + 33) * sizeof(float);
+  const size_t smem = (size_t)(2 * rank + D + 2 * R + THREADS + 33) * sizeof(float);
   if (dtype == IERT_F32)
     launch_dep(latent_attention_decode_kernel<float>, grid, dim3(THREADS), smem, stream, (const float*)q, ldq,
-               (const float*)w_uk, (const float*)w_uv, (float*)out, *batch, *kv, H, D, V, scale, sink, err);
+               (const float*)w_uk, (const float*)w_uv, (float*)out, *batch, *kv, H, D, R, V, scale, sink, gate, err);
   else if (dtype == IERT_BF16)
     launch_dep(latent_attention_decode_kernel<__nv_bfloat16>, grid, dim3(THREADS), smem, stream,
                (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)w_uk, (const __nv_bfloat16*)w_uv,
-               (__nv_bfloat16*)out, *batch, *kv, H, D, V, scale, sink, err);
+               (__nv_bfloat16*)out, *batch, *kv, H, D, R, V, scale, sink, gate, err);
   else return IERT_BAD_ARGUMENT;
   return iert_check_launch("latent_attention_decode");
+}
+
+// x: fp32 [T, ldx] = q [H * (D + R)] | latent [rank] | rotated key part [R] | gate logits [H] (if has_gate).
+// c_ext [T, rank + R], q_out [T, H * q_head] with row stride ldq (q_head >= D + R) in `dtype`; gate_out fp32 [T, H]; inv_freq fp32 [R / 2].
+// With `store` the rows of c_ext also go to the cache (kv_heads 1, head_dim rank + R, keys only).
+IERT_API int iert_latent_prep(const float* x, long long ldx, int H, int D, int R, int rank, const float* wkv, float eps,
+                              const float* inv_freq, int pairing, int has_gate, float out_scale, void* c_ext, void* q_out,
+                              long long ldq, int q_head, float* gate_out, int dtype, const IertBatchView* batch, const IertKvView* kv,
+                              int store, int* err, cudaStream_t stream) {
+  if (batch->n_tokens <= 0) return IERT_OK;
+  if (H <= 0 || D < 0 || R < 0 || (R & 1) || rank <= 0 || q_head < D + R || ldq < (long long)H * q_head || (R > 0 && !inv_freq) || (has_gate && !gate_out) ||
+      (pairing != IERT_PAIR_HALF && pairing != IERT_PAIR_INTERLEAVED) ||
+      (store && (kv->head_dim != rank + R || kv->kv_heads != 1 || kv->dtype != dtype)))
+    return IERT_BAD_ARGUMENT;
+  if (dtype == IERT_F32)
+    launch_dep(latent_prep_kernel<float>, dim3(batch->n_tokens), dim3(256), 0, stream, x, ldx, H, D, R, rank, wkv, eps, inv_freq,
+               pairing, has_gate, out_scale, (float*)c_ext, (float*)q_out, ldq, q_head, gate_out, *batch, *kv, store, err);
+  else if (dtype == IERT_BF16)
+    launch_dep(latent_prep_kernel<__nv_bfloat16>, dim3(batch->n_tokens), dim3(256), 0, stream, x, ldx, H, D, R, rank, wkv, eps,
+               inv_freq, pairing, has_gate, out_scale, (__nv_bfloat16*)c_ext, (__nv_bfloat16*)q_out, ldq, q_head, gate_out, *batch,
+               *kv, store, err);
+  else return IERT_BAD_ARGUMENT;
+  return iert_check_launch("latent_prep");
+}
+
+// attn [T, H * head] -> out [T, H * V] (V <= head), times gate [T, H] (fp32, optional).
+IERT_API int iert_head_gate_mul(const void* attn, int head, void* out, int V, int H, const float* gate, int dtype,
+                                int n_tokens, cudaStream_t stream) {
+  if (n_tokens <= 0) return IERT_OK;
+  if (H <= 0 || V <= 0 || head < V) return IERT_BAD_ARGUMENT;
+  if (dtype == IERT_F32)
+    launch_dep(head_gate_mul_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, (const float*)attn, head, (float*)out, V, H, gate);
+  else if (dtype == IERT_BF16)
+    launch_dep(head_gate_mul_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, stream, (const __nv_bfloat16*)attn, head,
+               (__nv_bfloat16*)out, V, H, gate);
+  else return IERT_BAD_ARGUMENT;
+  return iert_check_launch("head_gate_mul");
 }

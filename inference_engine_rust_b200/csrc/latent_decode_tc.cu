@@ -42,18 +42,20 @@ constexpr int ABSORB_THREADS = 256;
 
 __global__ void __launch_bounds__(ABSORB_THREADS)
 latent_absorb_q_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __nv_bfloat16* __restrict__ w_uk,
-                       __nv_bfloat16* __restrict__ qa, int H, int Hpad, int D, int rank) {
+                       __nv_bfloat16* __restrict__ qa, int H, int Hpad, int D, int R, int rank) {
   extern __shared__ float sm_q[];
   float* q_s = sm_q;                    // [D]
   float* part = sm_q + D;               // [4][rank]
   pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
-  __nv_bfloat16* dst = qa + ((size_t)t * Hpad + h) * rank;
+  __nv_bfloat16* dst = qa + ((size_t)t * Hpad + h) * (rank + R);
   if (h >= H) {
-    for (int r = threadIdx.x; r < rank; r += blockDim.x) dst[r] = __float2bfloat16_rn(0.f);
+    for (int r = threadIdx.x; r < rank + R; r += blockDim.x) dst[r] = __float2bfloat16_rn(0.f);
     return;
   }
-  for (int d = threadIdx.x; d < D; d += blockDim.x) q_s[d] = __bfloat162float(q[(size_t)t * ldq + (size_t)h * D + d]);
+  const __nv_bfloat16* qh = q + (size_t)t * ldq + (size_t)h * (D + R);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) q_s[d] = __bfloat162float(qh[d]);
+  for (int i = threadIdx.x; i < R; i += blockDim.x) dst[rank + i] = qh[D + i];      // the rotated part passes as it is
   __syncthreads();
   const int grp = threadIdx.x >> 6, lane64 = threadIdx.x & 63;
   const int d_lo = grp * ((D + 3) / 4), d_hi = min(D, d_lo + (D + 3) / 4);
@@ -82,11 +84,12 @@ latent_absorb_q_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const
 
 template <int MT>
 __global__ void __launch_bounds__(THREADS)
-latent_decode_tc_kernel(const __nv_bfloat16* __restrict__ qa, IertBatchView b, IertKvView kv, int Hpad, float scale,
+latent_decode_tc_kernel(const __nv_bfloat16* __restrict__ qa, IertBatchView b, IertKvView kv, int Hpad, int R, float scale,
                         int splits, float* __restrict__ part_m, float* __restrict__ part_l,
                         float* __restrict__ part_acc, int* __restrict__ err) {
   extern __shared__ __align__(16) uint8_t smem[];
-  const int rank = kv.head_dim, ldc = rank + 8;
+  // a cached row is `width` numbers: the latent (`rank`, which also serves as the value) and R rotated key numbers
+  const int width = kv.head_dim, rank = width - R, ldc = width + 8;
   __nv_bfloat16* qa_s = reinterpret_cast<__nv_bfloat16*>(smem);     // [MT*16][ldc]
   __nv_bfloat16* c_s = qa_s + MT * 16 * ldc;                         // [BK][ldc]
   __nv_bfloat16* p_s = c_s + BK * ldc;                               // [MT*16][PLD]
@@ -105,11 +108,11 @@ latent_decode_tc_kernel(const __nv_bfloat16* __restrict__ qa, IertBatchView b, I
     if (tid < MT * 16) { part_m[part_row0 + tid] = -INFINITY; part_l[part_row0 + tid] = 0.f; }
     return;
   }
-  const int chunks = rank / 8;                       // 16-byte pieces per row
+  const int chunks = width / 8;                      // 16-byte pieces per row
   for (int i = tid; i < MT * 16 * chunks; i += THREADS) {
     const int r = i / chunks, c = i - r * chunks;
     *reinterpret_cast<uint4*>(qa_s + r * ldc + c * 8) =
-        *reinterpret_cast<const uint4*>(qa + ((size_t)s * Hpad + rows0 + r) * rank + c * 8);
+        *reinterpret_cast<const uint4*>(qa + ((size_t)s * Hpad + rows0 + r) * width + c * 8);
   }
   float m_run[MT][2], l_run[MT][2], acc[MT][MAX_NTW][4];
 #pragma unroll
@@ -127,13 +130,13 @@ latent_decode_tc_kernel(const __nv_bfloat16* __restrict__ qa, IertBatchView b, I
     const int page = kv.page_table[(size_t)slot * kv.table_width + (tile % kv.ring_pages)];
     const bool page_ok = page >= 0 && page < kv.n_pages;
     if (!page_ok && tid == 0) atomicOr(err, IERT_ERR_PAGE_RANGE);
-    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(kv.k) + (size_t)(page_ok ? page : 0) * BK * rank;
+    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(kv.k) + (size_t)(page_ok ? page : 0) * BK * width;
     const int valid = page_ok ? min(BK, n_keys - tile * BK) : 0;     // rows beyond hold other sequences' leftovers
     for (int i = tid; i < BK * chunks; i += THREADS) {
       const int r = i / chunks, c = i - r * chunks;
       __nv_bfloat16* dst = c_s + r * ldc + c * 8;
       if (r < valid)
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src + (size_t)r * rank + c * 8));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src + (size_t)r * width + c * 8));
       else
         *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
     }
@@ -146,7 +149,7 @@ latent_decode_tc_kernel(const __nv_bfloat16* __restrict__ qa, IertBatchView b, I
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) sc[mt][nt][0] = sc[mt][nt][1] = sc[mt][nt][2] = sc[mt][nt][3] = 0.f;
-    for (int k0 = 0; k0 < rank; k0 += 16) {
+    for (int k0 = 0; k0 < width; k0 += 16) {
       uint32_t bf[2][2];
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
@@ -263,8 +266,8 @@ template <typename T>
 __global__ void __launch_bounds__(MERGE_THREADS)
 latent_decode_merge_kernel(const float* __restrict__ part_m, const float* __restrict__ part_l,
                            const float* __restrict__ part_acc, int splits, int Hpad, int rank,
-                           const float* __restrict__ sink, const T* __restrict__ w_uv, T* __restrict__ out,
-                           IertBatchView b, int H, int V) {
+                           const float* __restrict__ sink, const float* __restrict__ gate, const T* __restrict__ w_uv,
+                           T* __restrict__ out, IertBatchView b, int H, int V) {
   extern __shared__ float sm[];
   float* lat = sm;                 // [rank]
   float* wgt = sm + rank;          // [64]
@@ -338,13 +341,13 @@ latent_decode_merge_kernel(const float* __restrict__ part_m, const float* __rest
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       const float sum = warp_sum(a[k]);
-      if (lane == 0 && e0 + k < V) o[e0 + k] = from_f32<T>(sum);
+      if (lane == 0 && e0 + k < V) o[e0 + k] = from_f32<T>(gate ? sum * gate[(size_t)t * H + h] : sum);
     }
   }
 }
 
-size_t decode_smem(int mt, int rank) {
-  return (size_t)(mt * 16 + BK) * (rank + 8) * 2 + (size_t)mt * 16 * PLD * 2 + (size_t)8 * mt * 16 * 4;
+size_t decode_smem(int mt, int width) {
+  return (size_t)(mt * 16 + BK) * (width + 8) * 2 + (size_t)mt * 16 * PLD * 2 + (size_t)8 * mt * 16 * 4;
 }
 
 }  // namespace
@@ -364,25 +367,26 @@ IERT_API int iert_latent_decode_tc_plan(int n_seqs, int H, int table_width, int*
   return IERT_OK;
 }
 
-// q [T, ldq] bf16 (H*D per token, one token per sequence); w_uk [H*D, rank], w_uv [H*V, rank] bf16 row-major;
-// qa: scratch bf16 [T, Hpad, rank]; part_m, part_l: fp32 [T, splits, Hpad]; part_acc: fp32 [T, splits, Hpad, rank];
+// q [T, ldq] bf16 (H*(D+R) per token, one token per sequence: per head D unrotated and R rotated numbers); the cache's
+// rows are rank + R wide (latent | rotated key part); w_uk [H*D, rank], w_uv [H*V, rank] bf16 row-major; gate: fp32 [T, H]
+// or null.  qa: scratch bf16 [T, Hpad, rank + R]; part_m, part_l: fp32 [T, splits, Hpad]; part_acc: fp32 [T, splits, Hpad, rank];
 // out bf16 [T, H*V].  Hpad and splits as iert_latent_decode_tc_plan gives them.
 IERT_API int iert_latent_attention_decode_tc(const void* q, long long ldq, const void* w_uk, const void* w_uv, void* out,
-                                             const IertBatchView* batch, const IertKvView* kv, int H, int D, int V,
-                                             float scale, const float* sink, int Hpad, int splits, void* qa,
-                                             float* part_m, float* part_l, float* part_acc, int* err,
+                                             const IertBatchView* batch, const IertKvView* kv, int H, int D, int R, int V,
+                                             float scale, const float* sink, const float* gate, int Hpad, int splits,
+                                             void* qa, float* part_m, float* part_l, float* part_acc, int* err,
                                              cudaStream_t stream) {
-  const int T = batch->n_tokens, rank = kv->head_dim;
+  const int T = batch->n_tokens, width = kv->head_dim, rank = width - R;
   if (T <= 0) return IERT_OK;
-  if (T != batch->n_seqs || kv->dtype != IERT_BF16 || kv->kv_heads != 1 || kv->page_tokens != BK || rank % 32 ||
-      rank < 32 || rank > MAX_NTW * 32 || H <= 0 || Hpad % 16 || Hpad < H || Hpad > 65535 || splits < 1 || splits > 64 ||
+  if (T != batch->n_seqs || kv->dtype != IERT_BF16 || kv->kv_heads != 1 || kv->page_tokens != BK || rank % 32 || R < 0 ||
+      R % 16 || width > 640 || rank < 32 || rank > MAX_NTW * 32 || H <= 0 || Hpad % 16 || Hpad < H || Hpad > 65535 || splits < 1 || splits > 64 ||
       D <= 0 || D > 8192 || V <= 0 || (ldq % 8) || ((uintptr_t)q & 15))
     return IERT_BAD_ARGUMENT;
   const int mt = Hpad % 32 == 0 ? 2 : 1;
-  const size_t smem = decode_smem(mt, rank);
+  const size_t smem = decode_smem(mt, width);
   static bool configured = false;
   if (!configured) {
-    const int most = (int)decode_smem(2, MAX_NTW * 32);
+    const int most = (int)decode_smem(2, 640);
     if (cudaFuncSetAttribute(latent_decode_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
         cudaFuncSetAttribute(latent_decode_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess) {
       cudaGetLastError();
@@ -391,16 +395,16 @@ IERT_API int iert_latent_attention_decode_tc(const void* q, long long ldq, const
     configured = true;
   }
   launch_dep(latent_absorb_q_kernel, dim3(T, Hpad), dim3(ABSORB_THREADS), (size_t)(D + 4 * rank) * sizeof(float), stream,
-             (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)w_uk, (__nv_bfloat16*)qa, H, Hpad, D, rank);
+             (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)w_uk, (__nv_bfloat16*)qa, H, Hpad, D, R, rank);
   dim3 grid(T, splits, Hpad / (mt * 16));
   if (mt == 2)
-    launch_dep(latent_decode_tc_kernel<2>, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)qa, *batch, *kv, Hpad,
+    launch_dep(latent_decode_tc_kernel<2>, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)qa, *batch, *kv, Hpad, R,
                scale, splits, part_m, part_l, part_acc, err);
   else
-    launch_dep(latent_decode_tc_kernel<1>, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)qa, *batch, *kv, Hpad,
+    launch_dep(latent_decode_tc_kernel<1>, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)qa, *batch, *kv, Hpad, R,
                scale, splits, part_m, part_l, part_acc, err);
   launch_dep(latent_decode_merge_kernel<__nv_bfloat16>, dim3(T, H), dim3(MERGE_THREADS), (size_t)(rank + 64) * sizeof(float),
-             stream, (const float*)part_m, (const float*)part_l, (const float*)part_acc, splits, Hpad, rank, sink,
+             stream, (const float*)part_m, (const float*)part_l, (const float*)part_acc, splits, Hpad, rank, sink, gate,
              (const __nv_bfloat16*)w_uv, (__nv_bfloat16*)out, *batch, H, V);
   return iert_check_launch("latent_attention_decode_tc");
 }

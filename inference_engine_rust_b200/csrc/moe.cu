@@ -65,8 +65,12 @@ __global__ void router_topk_kernel(const float* __restrict__ z, long long ldz, c
 
 // one warp per token; shared memory: s[N], c[N], group score [groups], flags [N] (bytes).  Output e of token t is
 // z[t * ldz + e * lde]: rows of tokens (lde = 1) or rows of outputs (ldz = 1).
+//   score_mode   0: scores are the softmax over all N outputs; 1: every output's own sigmoid
+//   group_mode   0: a group's score is its best choice score; 1: the sum of its two best (of its one, if it has one)
+//   weights      chosen scores / (their sum + weight_eps) * weight_scale
 __global__ void router_grouped_kernel(const float* __restrict__ z, long long ldz, long long lde, const float* __restrict__ correction, int E,
-                                      int N, int top, int groups, int keep, float* __restrict__ wt, float* __restrict__ wid,
+                                      int N, int top, int groups, int keep, int score_mode, int group_mode, float weight_eps,
+                                      float weight_scale, float* __restrict__ wt, float* __restrict__ wid,
                                       int* __restrict__ idx, float* __restrict__ w) {
   extern __shared__ float rsm[];
   float* s = rsm;
@@ -77,12 +81,17 @@ __global__ void router_grouped_kernel(const float* __restrict__ z, long long ldz
   pdl_wait();
   const int t = blockIdx.x, lane = threadIdx.x, per = N / groups;
   const float* row = z + (size_t)t * ldz;
-  float m = -INFINITY;
-  for (int e = lane; e < N; e += 32) m = fmaxf(m, row[e * lde]);
-  m = warp_max(m);
-  float den = 0.f;
-  for (int e = lane; e < N; e += 32) { const float p = expf(row[e * lde] - m); s[e] = p; den += p; }
-  den = warp_sum(den);
+  float den = 1.f;
+  if (score_mode == 0) {
+    float m = -INFINITY;
+    for (int e = lane; e < N; e += 32) m = fmaxf(m, row[e * lde]);
+    m = warp_max(m);
+    den = 0.f;
+    for (int e = lane; e < N; e += 32) { const float p = expf(row[e * lde] - m); s[e] = p; den += p; }
+    den = warp_sum(den);
+  } else {
+    for (int e = lane; e < N; e += 32) s[e] = 1.0f / (1.0f + expf(-row[e * lde]));
+  }
   for (int e = lane; e < N; e += 32) {
     s[e] = s[e] / den;
     c[e] = s[e] + (correction ? correction[e] : 0.f);
@@ -90,9 +99,13 @@ __global__ void router_grouped_kernel(const float* __restrict__ z, long long ldz
   }
   __syncwarp();
   for (int g = lane; g < groups; g += 32) {
-    float best = -INFINITY;
-    for (int j = 0; j < per; ++j) best = fmaxf(best, c[g * per + j]);
-    gs[g] = best;
+    float best = -INFINITY, second = -INFINITY;
+    for (int j = 0; j < per; ++j) {
+      const float v = c[g * per + j];
+      if (v > best) { second = best; best = v; }
+      else if (v > second) second = v;
+    }
+    gs[g] = group_mode == 1 && per > 1 ? best + second : best;
   }
   __syncwarp();
   // the `keep` best groups, one after the other; a group that was taken is marked by NaN
@@ -144,7 +157,7 @@ __global__ void router_grouped_kernel(const float* __restrict__ z, long long ldz
   if (lane == 0) {
     float identity = 0.f;
     for (int k = 0; k < top; ++k) {
-      const float p = val[k] / (sum + 1e-20f);
+      const float p = val[k] / (sum + weight_eps) * weight_scale;
       if (chosen[k] < E) wt[(size_t)t * E + chosen[k]] = p;
       else if (chosen[k] < N) identity += p;
       idx[(size_t)t * top + k] = chosen[k] < N ? chosen[k] : -1;
@@ -197,15 +210,17 @@ IERT_API int iert_router_topk(const float* z, long long ldz, const float* bias, 
 
 // z: output e of token t at z[t * ldz + e * lde] (fp32).
 IERT_API int iert_router_grouped(const float* z, long long ldz, long long lde, const float* correction, int n_tokens, int E, int N, int top,
-                                 int groups, int keep, float* wt, float* wid, int* idx, float* w, cudaStream_t stream) {
+                                 int groups, int keep, int score_mode, int group_mode, float weight_eps, float weight_scale,
+                                 float* wt, float* wid, int* idx, float* w, cudaStream_t stream) {
   if (n_tokens <= 0) return IERT_OK;
+  if (score_mode < 0 || score_mode > 1 || group_mode < 0 || group_mode > 1) return IERT_BAD_ARGUMENT;
   if (E < 0 || N < E || N <= 0 || top <= 0 || top > MAX_TOP || groups <= 0 || N % groups || keep <= 0 || keep > groups ||
       top > keep * (N / groups))
     return IERT_BAD_ARGUMENT;
   const size_t smem = (size_t)(2 * N + groups) * sizeof(float) + (size_t)N;
   if (smem > 48 * 1024) return IERT_BAD_ARGUMENT;
-  launch_dep(router_grouped_kernel, dim3(n_tokens), dim3(32), smem, stream, z, ldz, lde, correction, E, N, top, groups, keep, wt, wid,
-             idx, w);
+  launch_dep(router_grouped_kernel, dim3(n_tokens), dim3(32), smem, stream, z, ldz, lde, correction, E, N, top, groups, keep, score_mode,
+             group_mode, weight_eps, weight_scale, wt, wid, idx, w);
   return iert_check_launch("router_grouped");
 }
 

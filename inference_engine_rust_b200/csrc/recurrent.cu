@@ -18,6 +18,8 @@
 //   mLSTM, per token:  m' = max(f + m, i);  S <- e^(f+m-m') S + e^(i-m') k v^T;  n likewise with k;
 //                      o = S^T q / (max(|n . q|, e^(-m')) + 1e-6),  m starts at 0
 //       with i = cap tanh((zi + bi) / cap),  f = logsigmoid(cap tanh((zf + bf) / cap))
+//   wkv (decay per key channel, a bonus for the current token), per token:
+//                      o = (S + diag(u) k v^T)^T r;  S <- diag(w) S + k v^T
 #include "common.cuh"
 
 #include <stdlib.h>
@@ -395,6 +397,118 @@ __global__ void __launch_bounds__(256 + LOADERS) mlstm_recur_kernel(MlstmArgs a,
   }
 }
 
+struct WkvArgs {
+  const float* x;        // [T, ld] fp32: r [H*DIM] | k [H*DIM] | v [H*V] | ... (the projections)
+  long long ld;
+  const float* decay;    // [T, H*DIM] fp32: w, the factor of each row of S
+  const float* u;        // [H, DIM] fp32: the current token's bonus
+  float* state;          // per slot at s_off: S [H, DIM, V]
+  long long state_stride, s_off;
+  float* o;              // [T, H*V] fp32
+  int H, V, cols;
+};
+
+template <int R>
+__global__ void __launch_bounds__(256 + LOADERS) wkv_recur_kernel(WkvArgs a, IertBatchView b) {
+  constexpr int RPT = (DIM + R - 1) / R;
+  __shared__ __align__(16) float r_s[2][CHUNK][DIM], k_s[2][CHUNK][DIM], w_s[2][CHUNK][DIM], v_s[2][CHUNK][256];
+  pdl_wait();
+  const int s = blockIdx.x, head = blockIdx.y, c0 = blockIdx.z * a.cols;
+  const int slot = b.slot_ids[s];
+  const int t0 = b.cu_q[s], t1 = b.cu_q[s + 1];
+  if (slot < 0 || t1 <= t0) return;
+  const int workers = blockDim.x - LOADERS;
+  const bool loader = (int)threadIdx.x >= workers;
+  const int col = threadIdx.x / R, r = threadIdx.x % R;
+  const int j = c0 + col;
+  const bool live = !loader && col < a.cols && j < a.V;
+  const int HD = a.H * DIM;
+  auto fetch = [&](int buf, int tc, int tid, int nthreads) {
+    const int n = min(CHUNK, t1 - tc);
+    if (DIM % 4 == 0 && a.ld % 4 == 0 && ((uintptr_t)a.x & 15) == 0 && ((uintptr_t)a.decay & 15) == 0) {     // 16-byte loads
+      // every load of the chunk is issued before the first is stored (a loader's loads are all it waits for)
+      constexpr int ITER = (CHUNK * (DIM / 4) + LOADERS - 1) / LOADERS;
+      float4 rv[ITER], kv[ITER], wv[ITER];
+#pragma unroll
+      for (int it = 0; it < ITER; ++it) {
+        const int x = tid + it * nthreads;
+        if (x < n * (DIM / 4)) {
+          const int tt = x / (DIM / 4), d = 4 * (x - tt * (DIM / 4));
+          const float* rowp = a.x + (size_t)(tc + tt) * a.ld + head * DIM + d;
+          rv[it] = *reinterpret_cast<const float4*>(rowp);
+          kv[it] = *reinterpret_cast<const float4*>(rowp + HD);
+          wv[it] = *reinterpret_cast<const float4*>(a.decay + (size_t)(tc + tt) * HD + head * DIM + d);
+        }
+      }
+#pragma unroll
+      for (int it = 0; it < ITER; ++it) {
+        const int x = tid + it * nthreads;
+        if (x < n * (DIM / 4)) {
+          const int tt = x / (DIM / 4), d = 4 * (x - tt * (DIM / 4));
+          *reinterpret_cast<float4*>(&r_s[buf][tt][d]) = rv[it];
+          *reinterpret_cast<float4*>(&k_s[buf][tt][d]) = kv[it];
+          *reinterpret_cast<float4*>(&w_s[buf][tt][d]) = wv[it];
+        }
+      }
+    } else {
+      for (int x = tid; x < n * DIM; x += nthreads) {
+        const int tt = x / DIM, d = x - tt * DIM;
+        const float* rowp = a.x + (size_t)(tc + tt) * a.ld + head * DIM + d;
+        r_s[buf][tt][d] = rowp[0];
+        k_s[buf][tt][d] = rowp[HD];
+        w_s[buf][tt][d] = a.decay[(size_t)(tc + tt) * HD + head * DIM + d];
+      }
+    }
+    for (int x = tid; x < n * a.cols; x += nthreads) {
+      const int tt = x / a.cols, cc = x - tt * a.cols;
+      v_s[buf][tt][cc] = c0 + cc < a.V ? a.x[(size_t)(tc + tt) * a.ld + 2 * HD + head * a.V + c0 + cc] : 0.f;
+    }
+  };
+  float* Sg = a.state + (size_t)slot * a.state_stride + a.s_off + (size_t)head * DIM * a.V;
+  float S[RPT], u[RPT];
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const int d = i * R + r;
+    S[i] = (live && d < DIM) ? Sg[(size_t)d * a.V + j] : 0.f;
+    u[i] = d < DIM ? a.u[head * DIM + d] : 0.f;
+  }
+  fetch(0, t0, threadIdx.x, blockDim.x);
+  __syncthreads();
+  int buf = 0;
+  for (int tc = t0; tc < t1; tc += CHUNK, buf ^= 1) {
+    const int n = min(CHUNK, t1 - tc);
+    if (loader) {
+      if (tc + CHUNK < t1) fetch(buf ^ 1, tc + CHUNK, threadIdx.x - workers, LOADERS);
+    } else {
+#pragma unroll
+      for (int tt = 0; tt < CHUNK; ++tt) {
+        if (tt >= n) break;
+        const float vj = live ? v_s[buf][tt][col] : 0.f;
+        float oq = 0.f;
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+          const int d = i * R + r;
+          const float kd = d < DIM ? k_s[buf][tt][d] : 0.f, rd = d < DIM ? r_s[buf][tt][d] : 0.f;
+          const float wd = d < DIM ? w_s[buf][tt][d] : 0.f;
+          const float kv = kd * vj;
+          oq = fmaf(rd, fmaf(u[i], kv, S[i]), oq);
+          S[i] = fmaf(wd, S[i], kv);
+        }
+        oq = group_sum<R>(oq);
+        if (live && r == 0) a.o[(size_t)(tc + tt) * a.H * a.V + (size_t)head * a.V + j] = oq;
+      }
+    }
+    __syncthreads();
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const int d = i * R + r;
+      if (d < DIM) Sg[(size_t)d * a.V + j] = S[i];
+    }
+  }
+}
+
 // Lanes per column: the fewest that give the device about eight warps per SM (at most 32), and columns per
 // CTA so that a CTA has up to 256 computing threads.  (Measured at 32 heads of 128 x 128, one prompt of 2,048
 // tokens: 8 lanes per column 1.08 ms, 16 lanes 0.91 ms, 32 lanes 1.42 ms per layer.)
@@ -437,6 +551,20 @@ IERT_API int iert_delta_recur(const float* qkv, const float* beta, const float* 
   const int threads = ((sp.cols * sp.lanes + 31) / 32) * 32 + LOADERS;
   IERT_BY_LANES(sp.lanes, launch_dep(delta_recur_kernel<RR>, grid, dim3(threads), 0, stream, a, *batch));
   return iert_check_launch("delta_recur");
+}
+
+// x: fp32 [T, ld] = r [H*DIM] | k [H*DIM] | v [H*V] | ...; decay fp32 [T, H*DIM]; u fp32 [H, DIM]; o fp32 [T, H*V].
+IERT_API int iert_wkv_recur(const float* x, long long ld, const float* decay, const float* u, float* state,
+                            long long state_stride, long long s_off, float* o, int H, int V, const IertBatchView* batch,
+                            cudaStream_t stream) {
+  if (batch->n_seqs <= 0 || batch->n_tokens <= 0) return IERT_OK;
+  if (H <= 0 || V <= 0 || H > 65535 || ld < (long long)2 * H * DIM + (long long)H * V) return IERT_BAD_ARGUMENT;
+  const Split sp = pick_split(batch->n_seqs, H, V);
+  WkvArgs a = {x, ld, decay, u, state, state_stride, s_off, o, H, V, sp.cols};
+  dim3 grid(batch->n_seqs, H, (V + sp.cols - 1) / sp.cols);
+  const int threads = ((sp.cols * sp.lanes + 31) / 32) * 32 + LOADERS;
+  IERT_BY_LANES(sp.lanes, launch_dep(wkv_recur_kernel<RR>, grid, dim3(threads), 0, stream, a, *batch));
+  return iert_check_launch("wkv_recur");
 }
 
 IERT_API int iert_mlstm_recur(const void* proj, int dtype, long long ld, const float* gates, long long gld,

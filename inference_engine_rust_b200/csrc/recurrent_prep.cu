@@ -12,6 +12,15 @@
 //
 // gated_head_norm: each head's read-out divided by its root mean square (eps inside the root),
 //   times a weight, times an activation of the gate projection, stored in the run's dtype.
+//
+// The kernels around the recurrence with a decay per key channel ("wkv"):
+//   token_shift   every token's input mixed with the input of the token in front of it, once per reader:
+//                 mixed[m][t] = h[t] + (h[t-1] - h[t]) * mu[m]; in front of a sequence's first token stands the row the
+//                 state keeps (zeros at the start of a sequence).  fp32 arithmetic, one rounding.
+//   wkv_decay     w[t, c] = exp(-exp(w0[c] + sum_l W2[c, l] tanh(z[t, l]))) from the small product z, all fp32;
+//                 the same launch leaves each sequence's last input row in the state (the shift has read the old one).
+//   wkv_finish    each head's read-out divided by its root mean square (eps inside the root), times a weight, times
+//                 silu of the fp32 gate projection, times a fixed factor, stored in the run's dtype.
 #include "common.cuh"
 
 using namespace iert;
@@ -125,7 +134,123 @@ __global__ void gated_head_norm_kernel(const float* __restrict__ o, const T* __r
   }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256)
+token_shift_kernel(const T* __restrict__ h, long long ldh, const float* __restrict__ state, long long state_stride,
+                   long long prev_off, const float* __restrict__ mu, int n_mix, int width, T* __restrict__ mixed,
+                   IertBatchView b) {
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int s = sequence_of_token(b, t);
+  const int slot = s >= 0 ? b.slot_ids[s] : -1;
+  const size_t plane = (size_t)b.n_tokens * width;
+  if (slot < 0) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+      for (int m = 0; m < n_mix; ++m) mixed[m * plane + (size_t)t * width + i] = from_f32<T>(0.f);
+    return;
+  }
+  const bool first = t == b.cu_q[s];
+  const float* kept = state + (size_t)slot * state_stride + prev_off;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float x = to_f32(h[(size_t)t * ldh + i]);
+    const float before = first ? kept[i] : to_f32(h[(size_t)(t - 1) * ldh + i]);
+    const float d = before - x;
+    for (int m = 0; m < n_mix; ++m) mixed[m * plane + (size_t)t * width + i] = from_f32<T>(fmaf(d, mu[(size_t)m * width + i], x));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+wkv_decay_kernel(const float* __restrict__ z, long long ldz, int L, const float* __restrict__ w2t, const float* __restrict__ w0,
+                 int C, float* __restrict__ decay, const T* __restrict__ h, long long ldh, int width,
+                 float* __restrict__ state, long long state_stride, long long prev_off, IertBatchView b) {
+  extern __shared__ float lora[];          // [L]
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int s = sequence_of_token(b, t);
+  const int slot = s >= 0 ? b.slot_ids[s] : -1;
+  if (slot < 0) return;
+  for (int l = threadIdx.x; l < L; l += blockDim.x) lora[l] = tanhf(z[(size_t)t * ldz + l]);
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float a = w0[c];
+    for (int l = 0; l < L; ++l) a = fmaf(w2t[(size_t)l * C + c], lora[l], a);
+    decay[(size_t)t * C + c] = expf(-expf(a));
+  }
+  if (t == b.cu_q[s + 1] - 1) {            // the sequence's last token of this step: the next step's row in front
+    float* kept = state + (size_t)slot * state_stride + prev_off;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) kept[i] = to_f32(h[(size_t)t * ldh + i]);
+  }
+}
+
+template <typename T>
+__global__ void wkv_finish_kernel(const float* __restrict__ o, const float* __restrict__ gate, long long ldg,
+                                  const float* __restrict__ w, float eps, float out_scale, T* __restrict__ out,
+                                  int n_tokens, int H, int V) {
+  pdl_wait();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= n_tokens * H) return;
+  const int t = warp / H, h = warp - t * H;
+  const float* x = o + ((size_t)t * H + h) * V;
+  float ss = 0.f;
+  for (int e = lane; e < V; e += 32) ss = fmaf(x[e], x[e], ss);
+  const float r = out_scale / sqrtf(warp_sum(ss) / (float)V + eps);
+  const float* g = gate + (size_t)t * ldg + (size_t)h * V;
+  T* y = out + ((size_t)t * H + h) * V;
+  for (int e = lane; e < V; e += 32) y[e] = from_f32<T>(x[e] * r * w[h * V + e] * silu_f(g[e]));
+}
+
 }  // namespace
+
+// h: [T, ldh] the step's input rows (run dtype); state: fp32 per slot, the kept row at prev_off; mu: fp32 [n_mix, width];
+// mixed: [n_mix, T, width] run dtype.
+IERT_API int iert_token_shift(const void* h, int dtype, long long ldh, const float* state, long long state_stride,
+                              long long prev_off, const float* mu, int n_mix, int width, void* mixed,
+                              const IertBatchView* batch, cudaStream_t stream) {
+  if (batch->n_tokens <= 0) return IERT_OK;
+  if (n_mix <= 0 || width <= 0) return IERT_BAD_ARGUMENT;
+  if (dtype == IERT_F32)
+    launch_dep(token_shift_kernel<float>, dim3(batch->n_tokens), dim3(256), 0, stream, (const float*)h, ldh, state, state_stride,
+               prev_off, mu, n_mix, width, (float*)mixed, *batch);
+  else if (dtype == IERT_BF16)
+    launch_dep(token_shift_kernel<__nv_bfloat16>, dim3(batch->n_tokens), dim3(256), 0, stream, (const __nv_bfloat16*)h, ldh, state,
+               state_stride, prev_off, mu, n_mix, width, (__nv_bfloat16*)mixed, *batch);
+  else return IERT_BAD_ARGUMENT;
+  return iert_check_launch("token_shift");
+}
+
+// z: fp32 [T, ldz] (L used); w2t: fp32 [L, C] (the second matrix, transposed); w0: fp32 [C]; decay: fp32 [T, C].
+// h / state as for iert_token_shift: the last row of every sequence is stored at prev_off.
+IERT_API int iert_wkv_decay(const float* z, long long ldz, int L, const float* w2t, const float* w0, int C, float* decay,
+                            const void* h, int dtype, long long ldh, int width, float* state, long long state_stride,
+                            long long prev_off, const IertBatchView* batch, cudaStream_t stream) {
+  if (batch->n_tokens <= 0) return IERT_OK;
+  if (L <= 0 || L > 8192 || C <= 0 || width <= 0) return IERT_BAD_ARGUMENT;
+  const size_t smem = (size_t)L * sizeof(float);
+  if (dtype == IERT_F32)
+    launch_dep(wkv_decay_kernel<float>, dim3(batch->n_tokens), dim3(256), smem, stream, z, ldz, L, w2t, w0, C, decay,
+               (const float*)h, ldh, width, state, state_stride, prev_off, *batch);
+  else if (dtype == IERT_BF16)
+    launch_dep(wkv_decay_kernel<__nv_bfloat16>, dim3(batch->n_tokens), dim3(256), smem, stream, z, ldz, L, w2t, w0, C, decay,
+               (const __nv_bfloat16*)h, ldh, width, state, state_stride, prev_off, *batch);
+  else return IERT_BAD_ARGUMENT;
+  return iert_check_launch("wkv_decay");
+}
+
+// o: fp32 [T, H*V]; gate: fp32 [T, ldg] (H*V used); w: fp32 [H*V]; out: [T, H*V] in `dtype`.
+IERT_API int iert_wkv_finish(const float* o, const float* gate, long long ldg, const float* w, float eps, float out_scale,
+                             void* out, int dtype, int n_tokens, int H, int V, cudaStream_t stream) {
+  if (n_tokens <= 0) return IERT_OK;
+  if (H <= 0 || V <= 0) return IERT_BAD_ARGUMENT;
+  const unsigned blocks = (unsigned)(((long long)n_tokens * H + 3) / 4);
+  if (dtype == IERT_F32)
+    launch_dep(wkv_finish_kernel<float>, dim3(blocks), dim3(128), 0, stream, o, gate, ldg, w, eps, out_scale, (float*)out, n_tokens, H, V);
+  else if (dtype == IERT_BF16)
+    launch_dep(wkv_finish_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, o, gate, ldg, w, eps, out_scale,
+               (__nv_bfloat16*)out, n_tokens, H, V);
+  else return IERT_BAD_ARGUMENT;
+  return iert_check_launch("wkv_finish");
+}
 
 IERT_API int iert_delta_prep(const void* proj, int dtype, long long ld, const float* gates, long long gld,
                              const float* conv_w, const float* A_log, const float* dt_bias, float* state,

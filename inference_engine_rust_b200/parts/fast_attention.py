@@ -27,7 +27,7 @@ def decode_splits(n_tokens: int, kv_heads: int, group: int, head_dim: int) -> in
     return max(1, min(_MAX_SPLITS, _slots(head_dim) // ctas))      # as many splits as stay one wave
 
 
-def wants_length_cut(pos0, kv_heads: int, group: int, window, page_tokens: int, head_dim: int) -> bool:
+def wants_length_cut(pos0, kv_heads: int, group: int, window, page_tokens: int, head_dim: int, chunk=None) -> bool:
     """Should a one-token step over sequences at these positions be cut by length (see
     `decode_parts`) rather than evenly?  Yes if the longest sequence reads over 1.3 times the
     average number of pages (an even cut ends when its CTAs do).  And yes if the batch alone
@@ -37,8 +37,9 @@ def wants_length_cut(pos0, kv_heads: int, group: int, window, page_tokens: int, 
     n = len(pos0)
     if n < 2:
         return False
-    if window:
-        pages = [p // page_tokens + 1 - max(0, p + 1 - window) // page_tokens for p in pos0]
+    if window or chunk:
+        first = [max(p + 1 - window if window else 0, p - p % chunk if chunk else 0, 0) for p in pos0]
+        pages = [p // page_tokens + 1 - f // page_tokens for p, f in zip(pos0, first)]
     else:
         pages = [p // page_tokens + 1 for p in pos0]
     longest, total = max(pages), sum(pages)
@@ -112,5 +113,5 @@ def apply(attn, qkv, out, ctx, cache_view, from_cache: bool) -> bool:
     if not from_cache:
         return B.attention_prefill(qkv, out, ctx.batch, attn.heads, attn.kv_heads, attn.head_dim,
                                    attn.window or 0, attn.scale, ctx.max_q_len, ctx.stream, err=rt.err, sink=sink,
-                                   softcap=softcap)
+                                   softcap=softcap, chunk=getattr(attn, "chunk", None) or 0)
     return False

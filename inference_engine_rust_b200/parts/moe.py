@@ -15,7 +15,8 @@ token.
 `GroupedMoE` (kind "grouped_moe") is the same with another router and another expert: scores are the softmax over ALL
 router outputs, the choice is made on score + a stored `correction`, restricted to the `keep` best of `groups` equal
 runs of neighbouring outputs (a run's score is its largest choice score), the weights are the chosen scores over
-their sum; the last `identity` router outputs stand for experts without tensors that return their input; the
+their sum; with `score: "sigmoid"` every output is scored by its own sigmoid instead, with `group_score: "top2_sum"` a
+run's score is the sum of its two largest choice scores, and `route_scale` / `out_scale` multiply the weights; the last `identity` router outputs stand for experts without tensors that return their input; the
 experts' activation is any member of the gated-activation family (`activation`, `limit`), and they have no
 shared expert and no router bias.
 """
@@ -113,6 +114,7 @@ class MoE(FeedForward):
 
 class GroupedMoE(MoE):
     graph_safe = True
+    takes_out_scale = True
 
     def __init__(self, spec, rt: Runtime):
         super().__init__(spec, rt)
@@ -120,6 +122,14 @@ class GroupedMoE(MoE):
         self.outputs = self.experts + self.identity
         self.groups = int(spec.get("groups") or 1)
         self.keep = int(spec.get("keep") or self.groups)
+        self.score = spec.get("score") or "softmax"
+        self.group_score = spec.get("group_score") or "max"
+        if self.score not in B.ROUTER_SCORES or self.group_score not in B.ROUTER_GROUP_SCORES:
+            raise ValueError(f"grouped_moe: score must be one of {sorted(B.ROUTER_SCORES)} and group_score one of "
+                             f"{sorted(B.ROUTER_GROUP_SCORES)}, got {self.score!r} and {self.group_score!r}")
+        self.weight_eps = float(spec.get("weight_eps", 1e-20))
+        # both factors multiply the routing weights (fp32), in which the feed-forward's result is linear
+        self.weight_scale = float(spec.get("route_scale", 1.0)) * float(spec.get("out_scale", 1.0))
         if self.shared_ff:
             raise ValueError("grouped_moe has no shared expert")
         if self.outputs % self.groups:
@@ -154,12 +164,14 @@ class GroupedMoE(MoE):
             # matrix takes the router's rows as its "tokens" and the tokens as the matrix it streams, 16 tokens per
             # CTA, and leaves the logits with a row per router output.
             z = ws.take("moe.logits_by_output", (N, T), torch.float32)
-            by_output = B.gemm_rows(self.router.weight, xn[:T], z, N, B.GEMM_STORE, self.rt.err, ctx.stream)
+            # the streamed "matrix" is the step's rows, which the norm in front has just written
+            by_output = B.gemm_rows(self.router.weight, xn[:T], z, N, B.GEMM_STORE, self.rt.err, ctx.stream, w_dynamic=True)
         if not by_output:
             z = ws.take("moe.logits", (T, N), torch.float32)
             self.router.apply(xn, z, T, ctx.stream)
         B.router_grouped(z, self.correction, T, E, N, self.top, self.groups, self.keep, wt, wid, idx, w, ctx.stream,
-                         by_output=by_output)
+                         by_output=by_output, score=self.score, group_score=self.group_score, weight_eps=self.weight_eps,
+                         weight_scale=self.weight_scale)
         return wt, (wid if self.identity else None)
 
 

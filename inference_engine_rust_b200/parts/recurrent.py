@@ -1,5 +1,5 @@
-"""Mixers that keep a matrix state per head instead of a cache of keys: the gated delta rule and the
-mLSTM.  The state (fp32) lives in the sequence's slot of the cache's state storage, starts at zero and
+"""Mixers that keep a matrix state per head instead of a cache of keys: the gated delta rule, the
+mLSTM and the recurrence with a decay per key channel and token shift ("wkv").  The state (fp32) lives in the sequence's slot of the cache's state storage, starts at zero and
 is carried from step to step; a prompt and a single token run the same kernels.
 
 Both: one product for the wide projections [q; k; v; g] (run dtype), one small product with fp32
@@ -150,5 +150,77 @@ class MLstm(Mixer):
         self.o.apply(out, residual, T, ctx.stream, add_residual=True)
 
 
+class Wkv(Mixer):
+    """Matrix state with a decay per key channel and token shift.  With h' the input row in front of a token's own h
+    (zeros in front of a sequence's first), each of r, k, v, g, w reads its own mix h + (h' - h) mu; r, k, v = W_r, W_k, W_v
+    of their mixes (heads x dim), gate = silu(W_g .); decay w = exp(-exp(W_w2 tanh(W_w1 .) + w0)) per head and key channel;
+    per head
+
+        o = (S + diag(u) k v^T)^T r;   S <- diag(w) S + k v^T
+
+    o / rms(o) per head times `norm` [heads * dim] times the gate (times `out_scale`), then W_o.  State per sequence:
+    S [heads, dim, dim] and the last input row.  The projections have fp32 outputs; shift, decay, state, read-out,
+    norm and gate are fp32."""
+    graph_safe = True
+    takes_out_scale = True
+    MIXES = ("r", "k", "v", "g", "w")
+
+    def __init__(self, spec, rt: Runtime):
+        self.rt = rt
+        self.hidden_size = int(spec["hidden_size"])
+        self.H, self.D = int(spec["heads"]), int(spec["dim"])
+        self.eps = float(spec["eps"])
+        self.out_scale = float(spec.get("out_scale", 1.0))
+        self.lora = spec.get("decay_rank")          # None: taken from the stored matrices
+        self.s_floats = self.H * self.D * self.D
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        h, hd = self.hidden_size, self.H * self.D
+        # the inner size of the decay's two matrices: the spec's `decay_rank`, or whatever the stored tensors have
+        L, free = (int(self.lora), False) if self.lora else (max(8, (h // 16 + 7) // 8 * 8), True)
+        out = {f"mu.{m}": TensorSpec((h,)) for m in self.MIXES}
+        out.update({"r": TensorSpec((hd, h)), "k": TensorSpec((hd, h)), "v": TensorSpec((hd, h)), "g": TensorSpec((hd, h)),
+                    "w1": TensorSpec((L, h), free_dims=(0,) if free else ()),
+                    "w2": TensorSpec((hd, L), free_dims=(1,) if free else ()), "w0": TensorSpec((hd,)), "u": TensorSpec((self.H, self.D)),
+                    "norm": TensorSpec((hd,), "ones_plus_normal"), "o": TensorSpec((h, hd))})
+        return out
+
+    def load(self, t: Mapping[str, torch.Tensor]) -> None:
+        self.mu = _f32(torch.stack([t[f"mu.{m}"] for m in self.MIXES], dim=0))
+        self.proj = [Linear(t[m], self.rt) for m in ("r", "k", "v", "g")]
+        self.L = t["w1"].shape[0]
+        if t["w2"].shape[1] != self.L:
+            raise ValueError(f"wkv: w1 has {self.L} rows but w2 has {t['w2'].shape[1]} columns")
+        self.w1 = Linear(_stack(self.rt, [t["w1"]], 4), self.rt)
+        self.w2t = _f32(t["w2"].to(torch.float32).t())
+        self.w0, self.u, self.norm = _f32(t["w0"]), _f32(t["u"]), _f32(t["norm"])
+        self.o = Linear(t["o"], self.rt)
+
+    def cache_request(self) -> StateRequest:
+        return StateRequest((self.s_floats + self.hidden_size,), torch.float32)
+
+    def weight_bytes(self) -> int:
+        return sum(p.nbytes() for p in self.proj) + self.w1.nbytes() + self.w2t.numel() * 4 + self.o.nbytes()
+
+    def forward(self, xn, residual, ctx: StepContext, cache_view, writes_cache: bool) -> None:
+        rt, ws, T, H, D = self.rt, self.rt.workspace, ctx.n_tokens, self.H, self.D
+        hd, state = H * D, cache_view.state
+        mixed = ws.take("wkv.mixed", (len(self.MIXES), T, self.hidden_size), rt.dtype)
+        B.token_shift(xn, state, self.s_floats, self.mu, mixed, ctx.batch, ctx.stream)
+        x = ws.take("wkv.proj", (T, 4 * hd), torch.float32)
+        for i, lin in enumerate(self.proj):
+            lin.apply(mixed[i], x[:, i * hd:(i + 1) * hd], T, ctx.stream)
+        z = ws.take("wkv.lora", (T, self.w1.out_features), torch.float32)
+        self.w1.apply(mixed[4], z, T, ctx.stream)
+        decay = ws.take("wkv.decay", (T, hd), torch.float32)
+        B.wkv_decay(z, self.L, self.w2t, self.w0, decay, xn, state, self.s_floats, ctx.batch, ctx.stream)
+        o = ws.take("wkv.readout", (T, hd), torch.float32)
+        B.wkv_recur(x, decay, self.u, state, 0, o, D, H, D, ctx.batch, ctx.stream)
+        out = ws.take("wkv.out", (T, hd), rt.dtype)
+        B.wkv_finish(o, x[:, 3 * hd:], self.norm, self.eps, self.out_scale, out, T, H, D, ctx.stream)
+        self.o.apply(out, residual, T, ctx.stream, add_residual=True, ctx=ctx)
+
+
+register_part("mixer", "wkv", Wkv)
 register_part("mixer", "gated_delta", GatedDelta)
 register_part("mixer", "mlstm", MLstm)

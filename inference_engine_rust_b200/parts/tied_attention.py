@@ -11,7 +11,8 @@ one of two norms, both fp32 and both without a mean:
 
 rotation by the mixer's position part (a plain rotary encoding: its constants are handed to the
 preparation kernel), scores (q . k) * scale, optionally capped (`softcap` c: s <- c tanh(s / c)), a sliding
-window, softmax, optionally with a sink (`sink: true`: one more term of score 0 in the denominator that carries
+window and / or a mask of chunks (`chunk` C: a position sees the earlier positions p with p // C equal to its own,
+chunks counted from the start of the sequence), softmax, optionally with a sink (`sink: true`: one more term of score 0 in the denominator that carries
 no value), W_o on the concatenated heads.  `out_scale` multiplies the mixer's result (it is applied to the
 values, in which the result is linear).
 
@@ -46,6 +47,7 @@ class TiedKVAttention(Mixer):
         self.kv_heads = int(spec["kv_heads"])
         self.head_dim = int(spec["head_dim"])
         self.window = spec.get("window")
+        self.chunk = spec.get("chunk")
         self.scale = float(spec["scale"])
         self.softcap = float(spec.get("softcap") or 0.0)
         self.eps = float(spec.get("eps", 0.0))
@@ -85,20 +87,20 @@ class TiedKVAttention(Mixer):
             self.wk = tensors["k.norm"].to(torch.float32).contiguous()
 
     def cache_request(self) -> KVRequest:
-        return KVRequest(self.kv_heads, self.head_dim, self.window)
+        return KVRequest(self.kv_heads, self.head_dim, self.window, chunk=self.chunk)
 
     def weight_bytes(self) -> int:
         return self.qk.nbytes() + self.o.nbytes()
 
     def cut_by_length_key(self):
-        return ("tied_attention", self.heads, self.kv_heads, self.head_dim, self.window, self.rt.fast)
+        return ("tied_attention", self.heads, self.kv_heads, self.head_dim, self.window, self.chunk, self.rt.fast)
 
     def cut_by_length(self, pos0, cache_view) -> bool:
         if not self.rt.fast or cache_view is None:
             return False
         from . import fast_attention
         return fast_attention.wants_length_cut(pos0, self.kv_heads, self.heads // self.kv_heads, self.window,
-                                               cache_view.group.page_tokens, self.head_dim)
+                                               cache_view.group.page_tokens, self.head_dim, chunk=self.chunk)
 
     def forward(self, xn, residual, ctx: StepContext, cache_view, writes_cache: bool) -> None:
         rt, ws, T = self.rt, self.rt.workspace, ctx.n_tokens

@@ -24,10 +24,17 @@ class TensorSpec:
     """What a part expects under one name.  `init` tells the random-weights mode how to
     fill it: "normal" = N(0, std); "ones_plus_normal" = 1 + N(0, std) (norm scales);
     "eye_plus_normal" = identity + N(0, std) (square mixing matrices); "int_table" = integers
-    (kept as int32)."""
+    (kept as int32).  `free_dims`: axes whose size the stored tensor decides (a size no configuration key
+    gives); `shape` holds there the size the random-weights mode makes."""
 
     shape: Tuple[int, ...]
     init: str = "normal"
+    free_dims: Tuple[int, ...] = ()
+
+    def accepts(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(
+            a == b or (i in self.free_dims and a > 0) for i, (a, b) in enumerate(zip(shape, self.shape)))
 
     @property
     def is_int(self) -> bool:
@@ -74,7 +81,7 @@ def check_source(expected: Mapping[str, TensorSpec], source: TensorSource, where
     wrong_shape, wrong_kind = [], []
     for name in want & have:
         dt, shape = source.describe(name)
-        if tuple(shape) != tuple(expected[name].shape):
+        if not expected[name].accepts(shape):
             wrong_shape.append((name, tuple(shape), tuple(expected[name].shape)))
         if expected[name].is_int and dt not in _INT_NAMES:
             wrong_kind.append((name, dt, "an integer table"))

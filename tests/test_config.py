@@ -63,7 +63,7 @@ def test_head_dim_must_be_derivable():
 def test_unknown_architecture_lists_known_ones():
     with pytest.raises(ConfigError) as e:
         config_from_dict(dict(TINY_A, architectures=["GemmaForCausalLM"]))
-    assert "MistralForCausalLM" in str(e.value) and known_architectures() == ["Kuvelix", "MistralForCausalLM", "Sifasun", "Vefulix"]
+    assert "MistralForCausalLM" in str(e.value) and known_architectures() == ["Kuvelix", "MistralForCausalLM", "Sifasun", "Vefulix", "Vufinex"]
 
 
 def test_round_trip_through_a_folder(tmp_path):
