@@ -108,6 +108,39 @@ PRESETS["kuvelix-12b-sizes"] = _kuvelix(5120, 131072, 40, 32, 8, 128, 128, 14336
 PRESETS["kuvelix-tiny"] = _kuvelix(80, 320, 4, 6, 2, 16, 24, 136, 5, 3, 3, 4, 3, 40, loop=(1, 3, 2))
 
 
+def _vufinex(width, vocab, layers, heads, kv_heads, dim, chunk, wkv_heads, wkv_dim, decay_rank, lat_dim, rot_dim, vdim, kv_rank,
+             experts, top, groups, keep, expert_ff, shared_from=None):
+    """A Vufinex configuration whose layers go round chunked attention, wkv, wkv, latent attention, each with a mixture of
+    experts; from layer `shared_from` on, layers run with the weights of the layer that many places before them."""
+    moe = {"kind": "moe", "expert": {"ff": expert_ff},
+           "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": groups, "keep": keep}}}
+    mixers = [
+        ("attention", {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                       "mask": {"size": chunk}, "rot": {"base": 10000.0, "dims": dim // 2}}),
+        ("wkv", {"heads": wkv_heads, "dim": wkv_dim, "decay_rank": decay_rank}),
+        ("wkv", {"heads": wkv_heads, "dim": wkv_dim, "decay_rank": decay_rank}),
+        ("latent_attention", {"heads": heads, "dim": lat_dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank,
+                              "scale": (lat_dim + rot_dim) ** -0.5, "rot": {"base": 10000.0, "dims": rot_dim}}),
+    ]
+    out = []
+    for i in range(layers):
+        entry = {"type": mixers[i % 4][0], "mixer": copy.deepcopy(mixers[i % 4][1]), "mlp": copy.deepcopy(moe)}
+        if shared_from is not None and i >= shared_from:
+            entry["weights_of"] = i - shared_from
+        out.append(entry)
+    return {"architecture": "Vufinex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.8,
+            "embedding": {"scale": 4.0}, "layers": out}
+
+
+# Vufinex at the width, head count, head size and total feed-forward size (16 experts of 896 = 14,336) of Mistral 7B (latent
+# attention with 128 unrotated and 64 rotated numbers per head over a latent of 512), and a tiny one that runs anywhere in
+# seconds (its last four layers run with the first four's weights).
+PRESETS["vufinex-7b-sizes"] = _vufinex(4096, 32000, 32, 32, 8, 128, 2048, 64, 64, 64, 128, 64, 128, 512, 16, 4, 4, 2, 896)
+# the same at the sizes of Mistral NeMo 12B (width 5,120, a vocabulary of 131,072)
+PRESETS["vufinex-12b-sizes"] = _vufinex(5120, 131072, 40, 32, 8, 128, 2048, 80, 64, 64, 128, 64, 128, 512, 16, 4, 4, 2, 896)
+PRESETS["vufinex-tiny"] = _vufinex(96, 320, 8, 4, 2, 16, 24, 3, 32, 8, 16, 8, 24, 40, 6, 2, 3, 2, 32, shared_from=4)
+
+
 def preset(name: str) -> dict:
     """A copy of the named configuration (a config.json-style dict)."""
     try:

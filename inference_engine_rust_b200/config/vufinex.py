@@ -96,9 +96,9 @@ def _latent(where: str, raw: Mapping[str, Any]) -> Dict[str, Any]:
     out = {key: _number(where, raw, key, int) for key in ("heads", "dim", "vdim", "kv_rank")}
     out["rot_dim"] = _number(where, raw, "rot_dim", int, positive=False)
     out["scale"] = _number(where, raw, "scale", float)
-    rot = _rot(where, raw, out["rot_dim"])
     if out["rot_dim"] < 0 or out["rot_dim"] % 2:
         raise ConfigError(f"config.json: {where}.rot_dim {out['rot_dim']} must be even and not negative")
+    rot = _rot(where, raw, 1 << 30)            # its size is judged against rot_dim below
     if out["rot_dim"]:
         if rot is None:
             raise ConfigError(f"config.json: {where}: required key 'rot' is missing")

@@ -144,10 +144,10 @@ def _declare(lib) -> None:
                                          c_float, P, P, P, S],
         "iert_latent_prep": [P, LL, c_int, c_int, c_int, c_int, P, c_float, P, c_int, c_int, c_float, P, P, LL, c_int, P, c_int,
                              POINTER(BatchView), POINTER(KvView), c_int, P, S],
-        "iert_head_gate_mul": [P, c_int, P, c_int, c_int, P, c_int, c_int, S],
+        "iert_head_gate_mul": [P, c_int, P, c_int, c_int, P, c_int, POINTER(BatchView), S],
         "iert_token_shift": [P, c_int, LL, P, LL, LL, P, c_int, c_int, P, POINTER(BatchView), S],
         "iert_wkv_decay": [P, LL, c_int, P, P, c_int, P, P, c_int, LL, c_int, P, LL, LL, POINTER(BatchView), S],
-        "iert_wkv_finish": [P, P, LL, P, c_float, c_float, P, c_int, c_int, c_int, c_int, S],
+        "iert_wkv_finish": [P, P, LL, P, c_float, c_float, P, c_int, POINTER(BatchView), c_int, c_int, S],
         "iert_latent_decode_tc_plan": [c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)],
         "iert_router_topk": [P, LL, P, c_int, c_int, c_int, P, P, P, S],
         "iert_moe_scale": [P, c_int, LL, P, c_int, c_int, c_int, P, P, LL, P, c_int, S],
@@ -713,10 +713,10 @@ def wkv_recur(x, decay, u, state, s_off: int, o, D: int, H: int, V: int, batch: 
                                                 state.stride(0), s_off, o.data_ptr(), H, V, byref(batch), stream), "wkv_recur")
 
 
-def wkv_finish(o, gate, w, eps: float, out_scale: float, out, n_tokens: int, H: int, V: int, stream) -> None:
+def wkv_finish(o, gate, w, eps: float, out_scale: float, out, batch: BatchView, H: int, V: int, stream) -> None:
     """out = o / rms(o) per head * w * silu(gate) * out_scale (gate: fp32 [T, >= H*V])."""
     check(core().iert_wkv_finish(o.data_ptr(), gate.data_ptr(), gate.stride(0), w.data_ptr(), eps, out_scale, out.data_ptr(),
-                                 dtype_code(out.dtype), n_tokens, H, V, stream), "wkv_finish")
+                                 dtype_code(out.dtype), byref(batch), H, V, stream), "wkv_finish")
 
 
 # ---------------------------------------------------------------------------------------
@@ -756,9 +756,9 @@ def latent_prep(x, H: int, D: int, R: int, rank: int, wkv, eps: float, inv_freq,
                                   err.data_ptr(), stream), "latent_prep")
 
 
-def head_gate_mul(attn, head: int, out, V: int, H: int, gate, n_tokens: int, stream) -> None:
+def head_gate_mul(attn, head: int, out, V: int, H: int, gate, batch: BatchView, stream) -> None:
     """out[t, h, :V] = attn[t, h, :V] * gate[t, h] for heads stored `head` numbers apart (gate None: a plain copy)."""
-    check(core().iert_head_gate_mul(attn.data_ptr(), head, out.data_ptr(), V, H, _ptr(gate), dtype_code(attn.dtype), n_tokens,
+    check(core().iert_head_gate_mul(attn.data_ptr(), head, out.data_ptr(), V, H, _ptr(gate), dtype_code(attn.dtype), byref(batch),
                                     stream), "head_gate_mul")
 
 

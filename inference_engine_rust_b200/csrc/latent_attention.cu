@@ -284,9 +284,14 @@ __global__ void latent_prep_kernel(const float* __restrict__ x, long long ldx, i
 // out[t, h, :V] = attn[t, h, :V] * gate[t, h]: drops the padding of heads of `head` numbers and applies the gate.
 template <typename T>
 __global__ void head_gate_mul_kernel(const T* __restrict__ attn, int head, T* __restrict__ out, int V, int H,
-                                     const float* __restrict__ gate) {
+                                     const float* __restrict__ gate, IertBatchView b) {
   pdl_wait();
   const int t = blockIdx.x;
+  const int s = sequence_of_token(b, t);
+  if (s < 0 || b.slot_ids[s] < 0) {        // padding: its attention rows may never have been written
+    for (int i = threadIdx.x; i < H * V; i += blockDim.x) out[(size_t)t * H * V + i] = from_f32<T>(0.f);
+    return;
+  }
   for (int i = threadIdx.x; i < H * V; i += blockDim.x) {
     const int h = i / V, e = i - h * V;
     const float g = gate ? gate[(size_t)t * H + h] : 1.f;
@@ -381,14 +386,15 @@ IERT_API int iert_latent_prep(const float* x, long long ldx, int H, int D, int R
 
 // attn [T, H * head] -> out [T, H * V] (V <= head), times gate [T, H] (fp32, optional).
 IERT_API int iert_head_gate_mul(const void* attn, int head, void* out, int V, int H, const float* gate, int dtype,
-                                int n_tokens, cudaStream_t stream) {
+                                const IertBatchView* batch, cudaStream_t stream) {
+  const int n_tokens = batch->n_tokens;
   if (n_tokens <= 0) return IERT_OK;
   if (H <= 0 || V <= 0 || head < V) return IERT_BAD_ARGUMENT;
   if (dtype == IERT_F32)
-    launch_dep(head_gate_mul_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, (const float*)attn, head, (float*)out, V, H, gate);
+    launch_dep(head_gate_mul_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, (const float*)attn, head, (float*)out, V, H, gate, *batch);
   else if (dtype == IERT_BF16)
     launch_dep(head_gate_mul_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, stream, (const __nv_bfloat16*)attn, head,
-               (__nv_bfloat16*)out, V, H, gate);
+               (__nv_bfloat16*)out, V, H, gate, *batch);
   else return IERT_BAD_ARGUMENT;
   return iert_check_launch("head_gate_mul");
 }

@@ -186,11 +186,16 @@ wkv_decay_kernel(const float* __restrict__ z, long long ldz, int L, const float*
 template <typename T>
 __global__ void wkv_finish_kernel(const float* __restrict__ o, const float* __restrict__ gate, long long ldg,
                                   const float* __restrict__ w, float eps, float out_scale, T* __restrict__ out,
-                                  int n_tokens, int H, int V) {
+                                  int n_tokens, int H, int V, IertBatchView b) {
   pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= n_tokens * H) return;
   const int t = warp / H, h = warp - t * H;
+  const int s = sequence_of_token(b, t);
+  if (s < 0 || b.slot_ids[s] < 0) {        // padding: nobody wrote its read-out
+    for (int e = lane; e < V; e += 32) out[((size_t)t * H + h) * V + e] = from_f32<T>(0.f);
+    return;
+  }
   const float* x = o + ((size_t)t * H + h) * V;
   float ss = 0.f;
   for (int e = lane; e < V; e += 32) ss = fmaf(x[e], x[e], ss);
@@ -239,15 +244,16 @@ IERT_API int iert_wkv_decay(const float* z, long long ldz, int L, const float* w
 
 // o: fp32 [T, H*V]; gate: fp32 [T, ldg] (H*V used); w: fp32 [H*V]; out: [T, H*V] in `dtype`.
 IERT_API int iert_wkv_finish(const float* o, const float* gate, long long ldg, const float* w, float eps, float out_scale,
-                             void* out, int dtype, int n_tokens, int H, int V, cudaStream_t stream) {
+                             void* out, int dtype, const IertBatchView* batch, int H, int V, cudaStream_t stream) {
+  const int n_tokens = batch->n_tokens;
   if (n_tokens <= 0) return IERT_OK;
   if (H <= 0 || V <= 0) return IERT_BAD_ARGUMENT;
   const unsigned blocks = (unsigned)(((long long)n_tokens * H + 3) / 4);
   if (dtype == IERT_F32)
-    launch_dep(wkv_finish_kernel<float>, dim3(blocks), dim3(128), 0, stream, o, gate, ldg, w, eps, out_scale, (float*)out, n_tokens, H, V);
+    launch_dep(wkv_finish_kernel<float>, dim3(blocks), dim3(128), 0, stream, o, gate, ldg, w, eps, out_scale, (float*)out, n_tokens, H, V, *batch);
   else if (dtype == IERT_BF16)
     launch_dep(wkv_finish_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, o, gate, ldg, w, eps, out_scale,
-               (__nv_bfloat16*)out, n_tokens, H, V);
+               (__nv_bfloat16*)out, n_tokens, H, V, *batch);
   else return IERT_BAD_ARGUMENT;
   return iert_check_launch("wkv_finish");
 }

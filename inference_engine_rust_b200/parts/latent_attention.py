@@ -156,7 +156,7 @@ class LatentAttention(Mixer):
                 own = B.KvView(k=None, v=None, page_table=None, table_width=0, ring_pages=1, page_tokens=1, n_pages=0,
                                kv_heads=H, head_dim=P, dtype=B.dtype_code(qkv.dtype), window=0, chunk=0)
                 B.attention_plain(qkv, attn, ctx.batch, own, H, self.scale, False, rt.err, ctx.stream)
-            B.head_gate_mul(attn, P, out, V, H, gate, T, ctx.stream)
+            B.head_gate_mul(attn, P, out, V, H, gate, ctx.batch, ctx.stream)
         else:
             done = False
             if rt.fast and q.dtype == torch.bfloat16 and ctx.kind == "decode":

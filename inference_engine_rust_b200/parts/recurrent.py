@@ -217,7 +217,7 @@ class Wkv(Mixer):
         o = ws.take("wkv.readout", (T, hd), torch.float32)
         B.wkv_recur(x, decay, self.u, state, 0, o, D, H, D, ctx.batch, ctx.stream)
         out = ws.take("wkv.out", (T, hd), rt.dtype)
-        B.wkv_finish(o, x[:, 3 * hd:], self.norm, self.eps, self.out_scale, out, T, H, D, ctx.stream)
+        B.wkv_finish(o, x[:, 3 * hd:], self.norm, self.eps, self.out_scale, out, ctx.batch, H, D, ctx.stream)
         self.o.apply(out, residual, T, ctx.stream, add_residual=True, ctx=ctx)
 
 

@@ -131,8 +131,9 @@ def latent_attention(h: Tensor, w: Mapping[str, Tensor], m: Mapping, eps: float,
     q = lin(h, w["q"]).view(T, H, d + r)
     down = lin(h, w["dkv"])
     c = rnd(unit_rms(down[:, :rank], eps) * w["dkv.norm"].float())
-    k_rot = rotate_neighbours(down[:, None, rank:], r, m["rot"]["base"])            # [T, 1, r]
-    q = torch.cat([q[..., :d], rotate_neighbours(q[..., d:], r, m["rot"]["base"])], dim=-1)
+    base = (m.get("rot") or {}).get("base", 1.0)
+    k_rot = rotate_neighbours(down[:, None, rank:], r, base)            # [T, 1, r]
+    q = torch.cat([q[..., :d], rotate_neighbours(q[..., d:], r, base)], dim=-1)
     k = torch.cat([lin(c, w["uk"]).view(T, H, d), k_rot.expand(T, H, r)], dim=-1)
     v = lin(c, w["uv"]).view(T, H, dv)
     o = masked_attention(rnd(q), rnd(k), rnd(v), m["scale"], lambda t, j: j <= t)
