@@ -444,19 +444,24 @@ def main() -> int:
     ap.add_argument("--kernels", action="store_true",
                     help="also time the dominant kernels one by one with CUDA events (projections and decode "
                          "attention at the decode batch, projections at the prefill length): key 'kernels'")
-    ap.add_argument("--design", default=None, choices=["vefulix", "sifasun", "kuvelix"],
+    ap.add_argument("--design", default=None, choices=["vefulix", "sifasun", "kuvelix", "vufinex"],
                     help="instead of the default workload: prefill and decode of that design at Mistral 7B's width, "
                          "depth (--layers, default 8) and feed-forward size beside Mistral 7B itself, with a table of "
                          "each step's kernels against what their bytes and FLOPs allow (one JSON line)")
     ap.add_argument("--design-sizes", default="7b", choices=["7b", "12b"],
-                    help="with --design sifasun or kuvelix: the sizes of Mistral 7B (default) or of Mistral NeMo 12B")
+                    help="with --design sifasun, kuvelix or vufinex: the sizes of Mistral 7B (default) or of Mistral NeMo 12B")
+    ap.add_argument("--design-beside", default="mistral", choices=["mistral", "vefulix"],
+                    help="with --design: the model that runs beside it at equal sizes, Mistral (default) or, at the 7B "
+                         "sizes, Vefulix (the other design with recurrences, latent attention and experts)")
     a = ap.parse_args()
 
     if a.design is not None and a.impl != "reference":
         from inference_engine_rust_b200 import bench_designs
-        if a.design_sizes == "12b" and a.design not in ("sifasun", "kuvelix"):
-            ap.error("--design-sizes 12b is there for --design sifasun and --design kuvelix only")
-        base = "7b-v0.1" if a.design_sizes == "7b" else "nemo-12b"
+        if a.design_sizes == "12b" and a.design not in ("sifasun", "kuvelix", "vufinex"):
+            ap.error("--design-sizes 12b is there for --design sifasun, kuvelix and vufinex only")
+        if a.design_beside == "vefulix" and (a.design_sizes != "7b" or a.design == "vefulix"):
+            ap.error("--design-beside vefulix is there for another design at the 7B sizes")
+        base = "vefulix-7b-sizes" if a.design_beside == "vefulix" else "7b-v0.1" if a.design_sizes == "7b" else "nemo-12b"
         print(json.dumps(bench_designs.compare(f"{a.design}-{a.design_sizes}-sizes", base, a.layers or 8, peaks(), a.batch, a.context,
                                                a.prefill_tokens, min(a.steps, 32), max(3, min(a.warmup, 4)))))
         return 0

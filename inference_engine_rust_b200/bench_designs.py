@@ -19,7 +19,8 @@ LAUNCHERS = ["embed_gather", "rmsnorm", "rope_kv_store", "silu_mul", "gemm_plain
              "attention_decode", "attention_plain", "streams_norm", "streams_expand", "softcap", "delta_prep", "delta_recur",
              "mlstm_recur", "gated_head_norm", "latent_norm_store", "latent_attention_prompt", "latent_attention_decode_tc",
              "latent_attention_decode", "router_topk", "moe_scale", "add_normed", "cast_rows", "scale_values", "qk_prep",
-             "rglru_conv", "rglru_gates", "rglru_scan", "qkv_prep", "gate_mul", "router_grouped", "gated_act_mul"]
+             "rglru_conv", "rglru_gates", "rglru_scan", "qkv_prep", "gate_mul", "router_grouped", "gated_act_mul",
+             "token_shift", "wkv_decay", "wkv_recur", "wkv_finish", "latent_prep", "head_gate_mul"]
 GEMMS = {"gemm_plain", "gemm_tc", "gemm_rows", "gemm_tc_scaled", "gemm_tc_gated", "gemm_tc_gated_scaled"}
 
 
@@ -53,6 +54,8 @@ class KernelClock:
                     label = f"{_name} [{N} x {K}]"
                     flops = 2.0 * M * N * K
                     nbytes = w.numel() * w.element_size() + M * K * x.element_size() + M * N * o.element_size()
+                elif _name == "attention_prefill":
+                    label = f"{_name} [head {args[5]}]"           # a model may run it at more than one head size
                 if out is not False:
                     self.records.append((label, a, b, flops, nbytes))
                 return out
@@ -80,8 +83,8 @@ class KernelClock:
             row = {"kernel": label, "calls": calls, "us": round(us, 1)}
             tensor = True
             base = label.split(" ")[0]
-            if base in model_costs:
-                f, tensor, nb = model_costs[base]
+            if label in model_costs or base in model_costs:
+                f, tensor, nb = model_costs[label if label in model_costs else base]
                 flops, nbytes = f * calls, nb * calls
             if flops or nbytes:
                 peak = pk["bf16_tflops"] if tensor else FP32_TFLOPS
@@ -160,6 +163,42 @@ def _costs(cfg: dict, T: int, n_seqs: int, ctx: int, prompt: bool) -> Dict[str, 
             r = mlp["router"]
             out["moe_scale"] = (0.0, False, T * (r["experts"] * mlp["expert"]["ff"] * 4 + (10 * H if r.get("identity") else 0)))
             out["router_grouped"] = (0.0, False, T * (r["experts"] + r.get("identity", 0)) * 8)
+    elif cfg.get("architecture") == "Vufinex":
+        H = cfg["width"]
+        out["rmsnorm"] = (0.0, False, T * H * 6)
+        by = {l["type"]: l["mixer"] for l in cfg["layers"]}
+        if "attention" in by:
+            m = by["attention"]
+            hd, kvd = m["heads"] * m["dim"], m["kv_heads"] * m["dim"]
+            C = (m.get("mask") or {}).get("size") or (1 << 30)
+            seen = sum(min(i % C, i) + 1 for i in range(T)) if prompt else 0          # (query, key) pairs inside the chunks
+            out[f"attention_prefill [head {m['dim']}]"] = (4.0 * hd * seen, True, T * (2 * hd + 2 * kvd) * 2)
+            out["attention_decode_tc"] = (0.0, False, n_seqs * (ctx % C + 1) * 2 * kvd * 2)
+            out["qk_prep"] = (0.0, False, T * ((hd + kvd) * 4 + (hd + 2 * kvd) * 2 + 2 * kvd * 2))
+        if "wkv" in by:
+            m = by["wkv"]
+            C, L = m["heads"] * m["dim"], m.get("decay_rank") or max(8, (H // 16 + 7) // 8 * 8)
+            state = 2 * 4 * n_seqs * C * m["dim"]
+            out["token_shift"] = (0.0, False, T * H * 12)
+            out["wkv_decay"] = (2.0 * T * C * L, False, T * (L + C) * 4 + L * C * 4)
+            out["wkv_recur"] = (7.0 * T * C * m["dim"], False, T * C * 5 * 4 + state)
+            out["wkv_finish"] = (0.0, False, T * C * 10)
+        if "latent_attention" in by:
+            m = by["latent_attention"]
+            P = -(-max(m["dim"] + m["rot_dim"], m["vdim"]) // 16) * 16
+            wide = m["kv_rank"] + m["rot_dim"]
+            row = m["heads"] * (m["dim"] + m["rot_dim"]) + wide + m["heads"]
+            out[f"attention_prefill [head {P}]"] = (4.0 * m["heads"] * P * T * (T + 1) / 2, True, T * 4 * m["heads"] * P * 2)
+            out["latent_prep"] = (0.0, False, T * (row * 4 + wide * 4 + m["heads"] * P * 2))
+            out["head_gate_mul"] = (0.0, False, T * m["heads"] * (P + m["vdim"]) * 2)
+            out["latent_attention_decode"] = out["latent_attention_decode_tc"] = (
+                2.0 * n_seqs * m["heads"] * ctx * (wide + m["kv_rank"]), True,
+                n_seqs * ctx * wide * 2 + m["heads"] * (m["dim"] + m["vdim"]) * m["kv_rank"] * 2)
+        mlp = next((l["mlp"] for l in cfg["layers"] if l["mlp"]), None)
+        if mlp:
+            r = mlp["router"]
+            out["moe_scale"] = (0.0, False, T * r["experts"] * mlp["expert"]["ff"] * 4)
+            out["router_grouped"] = (0.0, False, T * r["experts"] * 8)
     else:
         hd = cfg["num_attention_heads"] * cfg["head_dim"]
         kvd = cfg["num_key_value_heads"] * cfg["head_dim"]
@@ -255,7 +294,10 @@ def compare(design: str, baseline: str, layers: int, pk, batch: int, context: in
     from .config import preset
     a, b = preset(design), preset(baseline)
     a["layers"] = a["layers"][:layers]
-    b["num_hidden_layers"] = layers
+    if "layers" in b:                       # a baseline whose configuration lists its layers
+        b["layers"] = b["layers"][:layers]
+    else:
+        b["num_hidden_layers"] = layers
     t0 = time.time()
     res = {"design": design, "baseline": baseline, "layers": layers, "batch": batch, "context": context,
            "prefill_tokens": prefill_tokens, "steps": steps, "warmup": warmup, "dtype": "bf16",

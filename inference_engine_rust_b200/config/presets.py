@@ -133,11 +133,11 @@ def _vufinex(width, vocab, layers, heads, kv_heads, dim, chunk, wkv_heads, wkv_d
 
 
 # Vufinex at the width, head count, head size and total feed-forward size (16 experts of 896 = 14,336) of Mistral 7B (latent
-# attention with 128 unrotated and 64 rotated numbers per head over a latent of 512), and a tiny one that runs anywhere in
+# attention with 128 unrotated and 64 rotated numbers per head over a latent of 512; chunks of 8,192 positions), and a tiny one that runs anywhere in
 # seconds (its last four layers run with the first four's weights).
-PRESETS["vufinex-7b-sizes"] = _vufinex(4096, 32000, 32, 32, 8, 128, 2048, 64, 64, 64, 128, 64, 128, 512, 16, 4, 4, 2, 896)
+PRESETS["vufinex-7b-sizes"] = _vufinex(4096, 32000, 32, 32, 8, 128, 8192, 64, 64, 64, 128, 64, 128, 512, 16, 4, 4, 2, 896)
 # the same at the sizes of Mistral NeMo 12B (width 5,120, a vocabulary of 131,072)
-PRESETS["vufinex-12b-sizes"] = _vufinex(5120, 131072, 40, 32, 8, 128, 2048, 80, 64, 64, 128, 64, 128, 512, 16, 4, 4, 2, 896)
+PRESETS["vufinex-12b-sizes"] = _vufinex(5120, 131072, 40, 32, 8, 128, 8192, 80, 64, 64, 128, 64, 128, 512, 16, 4, 4, 2, 896)
 PRESETS["vufinex-tiny"] = _vufinex(96, 320, 8, 4, 2, 16, 24, 3, 32, 8, 16, 8, 24, 40, 6, 2, 3, 2, 32, shared_from=4)
 
 

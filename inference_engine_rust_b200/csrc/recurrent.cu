@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(256 + LOADERS) delta_recur_kernel(DeltaArgs a,
     const int n = min(CHUNK, t1 - tc);
     if (DIM % 4 == 0 && C % 4 == 0 && ((uintptr_t)a.qkv & 15) == 0) {       // 16-byte loads
       // every load of the chunk is issued before the first is stored (a loader's loads are all it waits for)
-      constexpr int ITER = (CHUNK * (DIM / 4) + LOADERS - 1) / LOADERS;
+      constexpr int ITER = (CHUNK * (DIM / 4) + LOADERS - 1) / LOADERS > 0 ? (CHUNK * (DIM / 4) + LOADERS - 1) / LOADERS : 1;
       float4 qv[ITER], kv[ITER];
 #pragma unroll
       for (int it = 0; it < ITER; ++it) {
@@ -207,7 +207,7 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(MlstmArgs a, IertBatchV
     const int n = min(SCHUNK, t1 - tc);
     if (sizeof(T) == 2 && DIM % 8 == 0 && a.ld % 8 == 0 && ((uintptr_t)a.proj & 15) == 0) {      // eight bf16 per load
       // every load of the chunk is issued before the first is converted and stored
-      constexpr int ITER = (SCHUNK * (DIM / 8) * 2 + 96 - 1) / 96;
+      constexpr int ITER = (SCHUNK * (DIM / 8) * 2 + 96 - 1) / 96 > 0 ? (SCHUNK * (DIM / 8) * 2 + 96 - 1) / 96 : 1;     // key sizes below 8 never take this branch
       uint4 raw[ITER];
 #pragma unroll
       for (int it = 0; it < ITER; ++it) {
@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(256 + LOADERS) mlstm_recur_kernel(MlstmArgs a,
     const int n = min(CHUNK, t1 - tc);
     if (sizeof(T) == 2 && DIM % 8 == 0 && a.ld % 8 == 0 && ((uintptr_t)a.proj & 15) == 0) {      // eight bf16 per load
       // every load of the chunk is issued before the first is converted and stored
-      constexpr int ITER = (CHUNK * (DIM / 8) * 2 + LOADERS - 1) / LOADERS;
+      constexpr int ITER = (CHUNK * (DIM / 8) * 2 + LOADERS - 1) / LOADERS > 0 ? (CHUNK * (DIM / 8) * 2 + LOADERS - 1) / LOADERS : 1;
       uint4 raw[ITER];
 #pragma unroll
       for (int it = 0; it < ITER; ++it) {
@@ -427,7 +427,7 @@ __global__ void __launch_bounds__(256 + LOADERS) wkv_recur_kernel(WkvArgs a, Ier
     const int n = min(CHUNK, t1 - tc);
     if (DIM % 4 == 0 && a.ld % 4 == 0 && ((uintptr_t)a.x & 15) == 0 && ((uintptr_t)a.decay & 15) == 0) {     // 16-byte loads
       // every load of the chunk is issued before the first is stored (a loader's loads are all it waits for)
-      constexpr int ITER = (CHUNK * (DIM / 4) + LOADERS - 1) / LOADERS;
+      constexpr int ITER = (CHUNK * (DIM / 4) + LOADERS - 1) / LOADERS > 0 ? (CHUNK * (DIM / 4) + LOADERS - 1) / LOADERS : 1;
       float4 rv[ITER], kv[ITER], wv[ITER];
 #pragma unroll
       for (int it = 0; it < ITER; ++it) {
