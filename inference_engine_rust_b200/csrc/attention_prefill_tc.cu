@@ -1,4 +1,4 @@
-// Prompt attention on the 5th-generation tensor cores (tcgen05) for head sizes 64 and 128:
+// Prompt attention on the 5th-generation tensor cores (tcgen05) for head sizes 64, 128, 192 and 256:
 // causal, optional sliding window, grouped heads, prompts of unequal lengths packed back to
 // back.  Scores and the output accumulate in tensor memory; queries, keys, values come by TMA
 // (128-byte swizzle) straight from the step's packed projection.
@@ -6,8 +6,10 @@
 //   grid (heads, query tiles, sequences); a CTA owns 128 consecutive queries of one head.  Blocks
 //   are handed out in index order, so all heads' longest tiles (the last queries) start first
 //   and the short ones fill the tail.
-//   Two CTAs share an SM (half of its shared memory, tensor memory and registers each), so one
-//   CTA's softmax overlaps the other's MMAs and loads.
+//   At head sizes 64 and 128 two CTAs share an SM (half of its shared memory, tensor memory and registers each), so
+//   one CTA's softmax overlaps the other's MMAs and loads; at 192 and 256 the output alone takes that many columns
+//   of tensor memory beside the two score buffers, a CTA asks for all 512 columns and has the SM to itself (its
+//   shared memory, 144 and 192 KB, would not let a second one in either).
 //   warp 4      TMA producer: the query tile once, then key and value tiles of 64 positions
 //               into a two-deep ring.
 //   warp 5      MMA issuer.  S = Q K^T  (128 x 64 x HEAD_DIM, both operands K-major) into one
@@ -31,10 +33,10 @@
 #include "tma_host.cuh"
 
 #ifndef HEAD_DIM
-#error "compile with -DHEAD_DIM=<64 or 128>"
+#error "compile with -DHEAD_DIM=<64, 128, 192 or 256>"
 #endif
 
-#if HEAD_DIM == 64 || HEAD_DIM == 128
+#if HEAD_DIM == 64 || HEAD_DIM == 128 || HEAD_DIM == 192 || HEAD_DIM == 256
 
 using namespace iert;
 using namespace sm100;
@@ -48,7 +50,7 @@ constexpr int SUB_BYTES = BM * 128;            // a block of the query / probabi
 constexpr int KV_SUB_BYTES = BN * 128;         // a block of a key / value tile: 64 rows x 128 bytes
 constexpr int THREADS = 192;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
-constexpr uint32_t TMEM_COLS = 256;            // S0 [0,64) S1 [64,128) O [128, 128 + HD): two CTAs share an SM
+constexpr uint32_t TMEM_COLS = HD <= 128 ? 256 : 512;   // S0 [0,64) S1 [64,128) O [128, 128 + HD); a power of two
 constexpr uint32_t O_COL = 128;
 
 struct PrefillTcParams {

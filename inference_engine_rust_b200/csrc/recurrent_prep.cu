@@ -151,6 +151,41 @@ token_shift_kernel(const T* __restrict__ h, long long ldh, const float* __restri
   }
   const bool first = t == b.cu_q[s];
   const float* kept = state + (size_t)slot * state_stride + prev_off;
+  if (sizeof(T) == 2 && width % 8 == 0 && ldh % 8 == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)mixed & 15) == 0 &&
+      ((uintptr_t)kept & 15) == 0 && ((uintptr_t)mu & 15) == 0) {
+    // eight numbers a thread: 16-byte loads of the row, the row in front and the factors, 16-byte stores per mix
+    for (int i = threadIdx.x * 8; i < width; i += blockDim.x * 8) {
+      float x[8], d[8];
+      {
+        const uint4 v = *reinterpret_cast<const uint4*>(h + (size_t)t * ldh + i);
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(p[e]); x[2 * e] = f.x; x[2 * e + 1] = f.y; }
+      }
+      if (first) {
+        const float4 a = *reinterpret_cast<const float4*>(kept + i), c = *reinterpret_cast<const float4*>(kept + i + 4);
+        d[0] = a.x - x[0]; d[1] = a.y - x[1]; d[2] = a.z - x[2]; d[3] = a.w - x[3];
+        d[4] = c.x - x[4]; d[5] = c.y - x[5]; d[6] = c.z - x[6]; d[7] = c.w - x[7];
+      } else {
+        const uint4 v = *reinterpret_cast<const uint4*>(h + (size_t)(t - 1) * ldh + i);
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(p[e]); d[2 * e] = f.x - x[2 * e]; d[2 * e + 1] = f.y - x[2 * e + 1]; }
+      }
+      for (int m = 0; m < n_mix; ++m) {
+        const float4 a = *reinterpret_cast<const float4*>(mu + (size_t)m * width + i);
+        const float4 c = *reinterpret_cast<const float4*>(mu + (size_t)m * width + i + 4);
+        uint4 out;
+        __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&out);
+        q[0] = __floats2bfloat162_rn(fmaf(d[0], a.x, x[0]), fmaf(d[1], a.y, x[1]));
+        q[1] = __floats2bfloat162_rn(fmaf(d[2], a.z, x[2]), fmaf(d[3], a.w, x[3]));
+        q[2] = __floats2bfloat162_rn(fmaf(d[4], c.x, x[4]), fmaf(d[5], c.y, x[5]));
+        q[3] = __floats2bfloat162_rn(fmaf(d[6], c.z, x[6]), fmaf(d[7], c.w, x[7]));
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(mixed) + m * plane + (size_t)t * width + i) = out;
+      }
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     const float x = to_f32(h[(size_t)t * ldh + i]);
     const float before = first ? kept[i] : to_f32(h[(size_t)(t - 1) * ldh + i]);
@@ -159,27 +194,75 @@ token_shift_kernel(const T* __restrict__ h, long long ldh, const float* __restri
   }
 }
 
+// A block takes DECAY_TOKENS tokens and 256 channels: a thread owns one channel, reads its column of the second matrix
+// once (eight loads in flight) and serves all the block's tokens from it, whose tanh rows stand in shared memory.
+constexpr int DECAY_TOKENS = 8;
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 wkv_decay_kernel(const float* __restrict__ z, long long ldz, int L, const float* __restrict__ w2t, const float* __restrict__ w0,
                  int C, float* __restrict__ decay, const T* __restrict__ h, long long ldh, int width,
                  float* __restrict__ state, long long state_stride, long long prev_off, IertBatchView b) {
-  extern __shared__ float lora[];          // [L]
+  extern __shared__ float lora[];          // [DECAY_TOKENS][L]
+  __shared__ int keep_slot[DECAY_TOKENS];  // the slot whose kept row token tt becomes (-1: none)
   pdl_wait();
-  const int t = blockIdx.x;
-  const int s = sequence_of_token(b, t);
-  const int slot = s >= 0 ? b.slot_ids[s] : -1;
-  if (slot < 0) return;
-  for (int l = threadIdx.x; l < L; l += blockDim.x) lora[l] = tanhf(z[(size_t)t * ldz + l]);
-  __syncthreads();
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float a = w0[c];
-    for (int l = 0; l < L; ++l) a = fmaf(w2t[(size_t)l * C + c], lora[l], a);
-    decay[(size_t)t * C + c] = expf(-expf(a));
+  const int t0 = blockIdx.x * DECAY_TOKENS, n = min(DECAY_TOKENS, b.n_tokens - t0);
+  if (threadIdx.x < DECAY_TOKENS) {
+    int slot = -1;
+    if ((int)threadIdx.x < n) {
+      const int t = t0 + threadIdx.x;
+      const int s = sequence_of_token(b, t);
+      // the sequence's last token of this step is the next step's row in front
+      if (s >= 0 && t == b.cu_q[s + 1] - 1) slot = b.slot_ids[s];
+    }
+    keep_slot[threadIdx.x] = slot;
   }
-  if (t == b.cu_q[s + 1] - 1) {            // the sequence's last token of this step: the next step's row in front
-    float* kept = state + (size_t)slot * state_stride + prev_off;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) kept[i] = to_f32(h[(size_t)t * ldh + i]);
+  for (int i = threadIdx.x; i < DECAY_TOKENS * L; i += blockDim.x) {
+    const int tt = i / L, l = i - tt * L;
+    lora[tt * L + l] = tt < n ? tanhf(z[(size_t)(t0 + tt) * ldz + l]) : 0.f;
+  }
+  __syncthreads();
+  const int c = blockIdx.y * 256 + threadIdx.x;
+  if (c < C) {
+    float a[DECAY_TOKENS];
+    const float bias = w0[c];
+#pragma unroll
+    for (int tt = 0; tt < DECAY_TOKENS; ++tt) a[tt] = bias;
+    int l = 0;
+    if ((L & 3) == 0) {                    // the tokens' rows by 16-byte shared-memory loads, eight weights in flight
+      for (; l + 8 <= L; l += 8) {
+        float w[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) w[k] = w2t[(size_t)(l + k) * C + c];
+#pragma unroll
+        for (int tt = 0; tt < DECAY_TOKENS; ++tt) {
+          const float4 x0 = *reinterpret_cast<const float4*>(lora + tt * L + l);
+          const float4 x1 = *reinterpret_cast<const float4*>(lora + tt * L + l + 4);
+          a[tt] = fmaf(w[0], x0.x, a[tt]); a[tt] = fmaf(w[1], x0.y, a[tt]); a[tt] = fmaf(w[2], x0.z, a[tt]); a[tt] = fmaf(w[3], x0.w, a[tt]);
+          a[tt] = fmaf(w[4], x1.x, a[tt]); a[tt] = fmaf(w[5], x1.y, a[tt]); a[tt] = fmaf(w[6], x1.z, a[tt]); a[tt] = fmaf(w[7], x1.w, a[tt]);
+        }
+      }
+    }
+    for (; l < L; ++l) {
+      const float w = w2t[(size_t)l * C + c];
+#pragma unroll
+      for (int tt = 0; tt < DECAY_TOKENS; ++tt) a[tt] = fmaf(w, lora[tt * L + l], a[tt]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < DECAY_TOKENS; ++tt)
+      if (tt < n) decay[(size_t)(t0 + tt) * C + c] = expf(-expf(a[tt]));
+  }
+  // the kept rows: every block of the token group takes a slice of the width; all loads before the first store
+  const int per = (width + gridDim.y - 1) / gridDim.y;
+  const int i1 = min(width, ((int)blockIdx.y + 1) * per);
+  for (int i = blockIdx.y * per + threadIdx.x; i < i1; i += blockDim.x) {
+    float v[DECAY_TOKENS];
+#pragma unroll
+    for (int tt = 0; tt < DECAY_TOKENS; ++tt)
+      if (keep_slot[tt] >= 0) v[tt] = to_f32(h[(size_t)(t0 + tt) * ldh + i]);
+#pragma unroll
+    for (int tt = 0; tt < DECAY_TOKENS; ++tt)
+      if (keep_slot[tt] >= 0) state[(size_t)keep_slot[tt] * state_stride + prev_off + i] = v[tt];
   }
 }
 
@@ -192,16 +275,43 @@ __global__ void wkv_finish_kernel(const float* __restrict__ o, const float* __re
   if (warp >= n_tokens * H) return;
   const int t = warp / H, h = warp - t * H;
   const int s = sequence_of_token(b, t);
+  T* y = out + ((size_t)t * H + h) * V;
   if (s < 0 || b.slot_ids[s] < 0) {        // padding: nobody wrote its read-out
-    for (int e = lane; e < V; e += 32) out[((size_t)t * H + h) * V + e] = from_f32<T>(0.f);
+    for (int e = lane; e < V; e += 32) y[e] = from_f32<T>(0.f);
     return;
   }
   const float* x = o + ((size_t)t * H + h) * V;
+  const float* g = gate + (size_t)t * ldg + (size_t)h * V;
+  if (sizeof(T) == 2 && V % 2 == 0 && V <= 512 && (ldg & 1) == 0 && ((uintptr_t)o & 7) == 0 && ((uintptr_t)gate & 7) == 0 &&
+      ((uintptr_t)w & 7) == 0 && ((uintptr_t)out & 3) == 0) {
+    // two numbers a lane and load: everything is asked for before the first sum
+    float2 xv[8], gv[8], wv[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int e = 2 * lane + 64 * k;
+      if (e < V) {
+        xv[k] = *reinterpret_cast<const float2*>(x + e);
+        gv[k] = *reinterpret_cast<const float2*>(g + e);
+        wv[k] = *reinterpret_cast<const float2*>(w + h * V + e);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (2 * lane + 64 * k < V) ss = fmaf(xv[k].x, xv[k].x, fmaf(xv[k].y, xv[k].y, ss));
+    const float r = out_scale / sqrtf(warp_sum(ss) / (float)V + eps);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int e = 2 * lane + 64 * k;
+      if (e < V)
+        *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(y) + e) =
+            __floats2bfloat162_rn(xv[k].x * r * wv[k].x * silu_f(gv[k].x), xv[k].y * r * wv[k].y * silu_f(gv[k].y));
+    }
+    return;
+  }
   float ss = 0.f;
   for (int e = lane; e < V; e += 32) ss = fmaf(x[e], x[e], ss);
   const float r = out_scale / sqrtf(warp_sum(ss) / (float)V + eps);
-  const float* g = gate + (size_t)t * ldg + (size_t)h * V;
-  T* y = out + ((size_t)t * H + h) * V;
   for (int e = lane; e < V; e += 32) y[e] = from_f32<T>(x[e] * r * w[h * V + e] * silu_f(g[e]));
 }
 
@@ -230,13 +340,14 @@ IERT_API int iert_wkv_decay(const float* z, long long ldz, int L, const float* w
                             const void* h, int dtype, long long ldh, int width, float* state, long long state_stride,
                             long long prev_off, const IertBatchView* batch, cudaStream_t stream) {
   if (batch->n_tokens <= 0) return IERT_OK;
-  if (L <= 0 || L > 8192 || C <= 0 || width <= 0) return IERT_BAD_ARGUMENT;
-  const size_t smem = (size_t)L * sizeof(float);
+  if (L <= 0 || L > 1024 || C <= 0 || width <= 0) return IERT_BAD_ARGUMENT;
+  const size_t smem = (size_t)DECAY_TOKENS * L * sizeof(float);
+  const dim3 grid((batch->n_tokens + DECAY_TOKENS - 1) / DECAY_TOKENS, (C + 255) / 256);
   if (dtype == IERT_F32)
-    launch_dep(wkv_decay_kernel<float>, dim3(batch->n_tokens), dim3(256), smem, stream, z, ldz, L, w2t, w0, C, decay,
+    launch_dep(wkv_decay_kernel<float>, grid, dim3(256), smem, stream, z, ldz, L, w2t, w0, C, decay,
                (const float*)h, ldh, width, state, state_stride, prev_off, *batch);
   else if (dtype == IERT_BF16)
-    launch_dep(wkv_decay_kernel<__nv_bfloat16>, dim3(batch->n_tokens), dim3(256), smem, stream, z, ldz, L, w2t, w0, C, decay,
+    launch_dep(wkv_decay_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, z, ldz, L, w2t, w0, C, decay,
                (const __nv_bfloat16*)h, ldh, width, state, state_stride, prev_off, *batch);
   else return IERT_BAD_ARGUMENT;
   return iert_check_launch("wkv_decay");

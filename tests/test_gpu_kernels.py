@@ -526,7 +526,8 @@ def test_sampling_temperature_follows_the_cdf(vocab, temperature):
 
 @pytest.mark.parametrize("heads,kvh,hd,window", [(4, 2, 16, 16), (6, 1, 32, None), (3, 3, 48, 70), (8, 2, 128, None),
                                                  (4, 4, 128, 100), (5, 5, 80, 33), (2, 1, 256, 130), (6, 2, 64, None),
-                                                 (3, 1, 64, 200), (2, 2, 128, 129)])
+                                                 (3, 1, 64, 200), (2, 2, 128, 129), (4, 2, 192, None), (2, 2, 192, 150),
+                                                 (3, 1, 256, None)])
 def test_attention_prefill_against_plain_kernel(heads, kvh, hd, window):
     """The tensor-core prompt attention against its plain sibling: unequal prompts (a single
     token, lengths around the 64-wide tiles, several tiles), windows that cut tiles at odd
