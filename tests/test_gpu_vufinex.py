@@ -230,10 +230,14 @@ def test_router_against_the_plain_choice(E, top, groups, keep, scale):
             torch.testing.assert_close(wt.cpu(), dense, rtol=1e-5, atol=1e-6)
 
 
-@pytest.mark.parametrize("H,D,T0,T1", [(2, 16, 5, 9), (1, 64, 1, 70), (3, 32, 33, 1), (2, 128, 3, 4)])
-def test_recurrence_against_the_plain_loop(H, D, T0, T1):
+@pytest.mark.parametrize("lanes", [None, 1, 4, 8, 32])
+@pytest.mark.parametrize("H,D,T0,T1", [(2, 16, 5, 9), (1, 64, 1, 70), (3, 32, 33, 1), (2, 128, 3, 4), (2, 12, 7, 2)])
+def test_recurrence_against_the_plain_loop(H, D, T0, T1, lanes, monkeypatch):
     """The state update and the read-out of the wkv recurrence alone, over two steps of one sequence (the second
-    continues from the state the first left) beside a second sequence of another length."""
+    continues from the state the first left) beside a second sequence of another length; with the lanes per column
+    of the state that the launcher picks, and with forced ones (a lane's rows lie apart or side by side)."""
+    if lanes is not None:
+        monkeypatch.setenv("IERT_RECURRENT_LANES", str(lanes))
     b = B()
     g = torch.Generator().manual_seed(H * D + T0)
     lens = [(T0, T1), (T1 + 2, 1)]
