@@ -274,19 +274,15 @@ __global__ void wkv_finish_kernel(const float* __restrict__ o, const float* __re
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= n_tokens * H) return;
   const int t = warp / H, h = warp - t * H;
-  const int s = sequence_of_token(b, t);
   T* y = out + ((size_t)t * H + h) * V;
-  if (s < 0 || b.slot_ids[s] < 0) {        // padding: nobody wrote its read-out
-    for (int e = lane; e < V; e += 32) y[e] = from_f32<T>(0.f);
-    return;
-  }
   const float* x = o + ((size_t)t * H + h) * V;
   const float* g = gate + (size_t)t * ldg + (size_t)h * V;
-  if (sizeof(T) == 2 && V % 2 == 0 && V <= 512 && (ldg & 1) == 0 && ((uintptr_t)o & 7) == 0 && ((uintptr_t)gate & 7) == 0 &&
-      ((uintptr_t)w & 7) == 0 && ((uintptr_t)out & 3) == 0) {
-    // two numbers a lane and load: everything is asked for before the first sum
-    float2 xv[8], gv[8], wv[8];
-    float ss = 0.f;
+  const bool wide = sizeof(T) == 2 && V % 2 == 0 && V <= 512 && (ldg & 1) == 0 && ((uintptr_t)o & 7) == 0 &&
+                    ((uintptr_t)gate & 7) == 0 && ((uintptr_t)w & 7) == 0 && ((uintptr_t)out & 3) == 0;
+  // two numbers a lane and load, all asked for before anything waits (also before the look-up of the token's sequence
+  // below: a padding token's rows hold leftovers, which are read and dropped)
+  float2 xv[8], gv[8], wv[8];
+  if (wide) {
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       const int e = 2 * lane + 64 * k;
@@ -296,6 +292,14 @@ __global__ void wkv_finish_kernel(const float* __restrict__ o, const float* __re
         wv[k] = *reinterpret_cast<const float2*>(w + h * V + e);
       }
     }
+  }
+  const int s = sequence_of_token(b, t);
+  if (s < 0 || b.slot_ids[s] < 0) {        // padding: nobody wrote its read-out
+    for (int e = lane; e < V; e += 32) y[e] = from_f32<T>(0.f);
+    return;
+  }
+  if (wide) {
+    float ss = 0.f;
 #pragma unroll
     for (int k = 0; k < 8; ++k)
       if (2 * lane + 64 * k < V) ss = fmaf(xv[k].x, xv[k].x, fmaf(xv[k].y, xv[k].y, ss));

@@ -106,10 +106,10 @@ ODD = config([layer("latent_attention", latent(heads=3, dim=10, rot_dim=6, vdim=
               layer("attention", attn(heads=3, kv_heads=3, dim=12, rot_dims=6, chunk=37), moe(experts=4, top=1, count=2, keep=1, ff=7))],
              width=52, vocab=75, eps=1e-6, mult=1.0, embed=1.0)
 # sizes the tensor-core kernels take: tcgen05 prompt attention at head size 64, the one-token latent kernel
-TENSOR = config([layer("wkv", wkv(heads=2, dim=64, rank=16), moe(experts=8, top=3, count=2, keep=1, ff=64)),
-                 layer("attention", attn(heads=4, kv_heads=2, dim=64, scale=0.3, rot_dims=32, chunk=80), moe(experts=8, top=3, count=2, keep=1, ff=64)),
+TENSOR = config([layer("wkv", wkv(heads=2, dim=64, rank=24), moe(experts=6, top=2, count=3, keep=2, ff=48)),
+                 layer("attention", attn(heads=4, kv_heads=2, dim=64, scale=0.3, rot_dims=32, chunk=80), moe(experts=6, top=2, count=3, keep=2, ff=48)),
                  layer("latent_attention", latent(heads=4, dim=32, rot_dim=16, vdim=48, kv_rank=64, scale=0.25), moe(experts=8, top=2, count=4, keep=2, ff=32)),
-                 layer("attention", attn(heads=4, kv_heads=2, dim=64, scale=0.3, rot_dims=32, chunk=80), moe(experts=8, top=3, count=2, keep=1, ff=64), weights_of=1)],
+                 layer("attention", attn(heads=4, kv_heads=2, dim=64, scale=0.3, rot_dims=32, chunk=80), moe(experts=6, top=2, count=3, keep=2, ff=48), weights_of=1)],
                 width=128, vocab=160, mult=0.5, embed=6.0)
 WIDE_HEADS = config([layer("attention", attn(heads=2, kv_heads=1, dim=128, scale=0.2, rot_dims=64, chunk=130), moe(experts=4, top=2, count=2, keep=1, ff=32)),
                      layer("latent_attention", latent(heads=2, dim=64, rot_dim=32, vdim=128, kv_rank=96, scale=0.2), None),
