@@ -173,7 +173,7 @@ def load_library(name: str, sources: Sequence[str], defines: Sequence[str] = ())
 
 # Head sizes whose prompt-attention library is built ahead of time by build_all(); any other
 # multiple of 16 up to 256 is compiled the first time a model with that head size runs.
-PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 128)
+PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 128, 192)
 
 
 def attention_library(head_dim: int):
@@ -185,7 +185,7 @@ def attention_library(head_dim: int):
 
 # Key sizes whose recurrence library is built ahead of time by build_all(); any other size is compiled
 # the first time a model with that size runs.
-PREBUILT_RECURRENT_DIMS = (64, 128)
+PREBUILT_RECURRENT_DIMS = (32, 64, 128)
 
 
 def recurrent_library(dim: int):
